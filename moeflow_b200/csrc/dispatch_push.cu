@@ -1,0 +1,107 @@
+// Dispatch: pack + all-to-all in one kernel, over peer memory.
+//
+// Token t of source rank s bound for owner rank d always lands in row recv_d[s, t] (fixed position,
+// no count exchange).  A row is
+//     [ H bf16 hidden lanes | K int32 local expert ids | K fp32 routing weights | int32 valid ]
+// with a row pitch padded to a multiple of 16 bytes.  Slots whose expert lives on another rank carry
+// id -1 and weight 0; valid = 1 iff at least one slot is on d and t is a live token (t < T and
+// t < *num_valid).  Rows t >= T get valid = 0 and all-empty slots; their hidden lanes stay stale.
+//
+// The kernel writes every row straight into the owner's receive buffer with plain 16-byte stores
+// through the peer mapping (NVLink), then the last CTA to finish publishes this forward's epoch
+// in every owner's flag word [s] with a system-scope release store.  No NCCL call, no staging buffer.
+//
+// Replaces the reference's pack kernel plus its dispatch all_to_all_single
+// (moeflow/kernels/dispatch_pack.py:10-95, moeflow/fixed.py:95-125,234).
+#include "common.cuh"
+#include "moeflow_b200.h"
+
+namespace mf {
+
+constexpr int kDispatchThreads = 256;
+constexpr int kMaxTopK = 32;
+
+__global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const mf_dispatch_args a) {
+  __shared__ int s_id[kMaxTopK];
+  __shared__ float s_w[kMaxTopK];
+  __shared__ int s_present;
+
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  const unsigned epoch_next = *a.epoch + 1u;
+  const bool has_token = t < a.T;
+  const bool live = has_token && (a.num_valid == nullptr || t < *a.num_valid);
+
+  if (tid < a.K) {
+    s_id[tid] = has_token ? a.ids[(size_t)t * a.K + tid] : -1;
+    s_w[tid] = has_token ? a.weights[(size_t)t * a.K + tid] : 0.f;
+  }
+  __syncthreads();
+
+  // The hidden row is read once and kept in registers for all destinations.
+  const int chunks = a.H / 8;  // 16-byte chunks
+  constexpr int kMaxPerThread = 4;  // H <= 8192
+  uint4 xv[kMaxPerThread];
+  if (has_token) {
+    const uint4* xr = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.x) + (size_t)t * a.H);
+#pragma unroll
+    for (int i = 0; i < kMaxPerThread; ++i) {
+      const int c = tid + i * kDispatchThreads;
+      if (c < chunks) xv[i] = xr[c];
+    }
+  }
+
+  for (int d = 0; d < a.R; ++d) {
+    if (tid == 0) {
+      int present = 0;
+      if (live)
+        for (int k = 0; k < a.K; ++k) present |= (s_id[k] >= 0 && s_id[k] / a.L == d) ? 1 : 0;
+      s_present = present;
+      a.hit[(size_t)t * a.R + d] = (unsigned char)present;
+    }
+    __syncthreads();
+    const int present = s_present;
+    uint8_t* row = reinterpret_cast<uint8_t*>(a.peer_recv[d]) + ((size_t)a.rank * a.C + t) * a.pitch;
+    if (has_token && (present || !a.skip_payload)) {
+      uint4* dst = reinterpret_cast<uint4*>(row);
+#pragma unroll
+      for (int i = 0; i < kMaxPerThread; ++i) {
+        const int c = tid + i * kDispatchThreads;
+        if (c < chunks) dst[c] = xv[i];
+      }
+    }
+    int* meta = reinterpret_cast<int*>(row + (size_t)a.H * 2);
+    if (tid < a.K) {
+      const bool on = present && s_id[tid] >= 0 && s_id[tid] / a.L == d;
+      meta[tid] = on ? s_id[tid] - d * a.L : -1;
+      meta[a.K + tid] = on ? __float_as_int(s_w[tid]) : 0;
+    } else if (tid == a.K) {
+      meta[2 * a.K] = present;
+    }
+    __syncthreads();
+  }
+
+  // Publish: every thread's stores are fenced at system scope, then the CTA counts itself done.
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned done = atomicAdd(a.done_counter, 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence_system();
+      *a.done_counter = 0u;
+      *a.epoch = epoch_next;
+      for (int d = 0; d < a.R; ++d)
+        st_release_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, epoch_next);
+    }
+  }
+}
+
+}  // namespace mf
+
+extern "C" int mf_dispatch_push(const mf_dispatch_args* a, mf_stream_t stream) {
+  if (!a || a->C < 1 || a->T > a->C || a->K > mf::kMaxTopK || a->H % 8 != 0 ||
+      a->H / 8 > mf::kDispatchThreads * 4 || (a->pitch & 15) != 0 || a->pitch < (long long)a->H * 2 + (2 * a->K + 1) * 4)
+    return -1;
+  mf::dispatch_push_kernel<<<a->C, mf::kDispatchThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,200 @@
+// Expert metadata: from the received rows build, on the device and in one launch,
+//   * offsets[L+1]: entries of local expert e are [offsets[e], offsets[e+1]) in expert-major order,
+//     stable in (row, slot);
+//   * entry_row / entry_slot / entry_w for every expert-major position, and the inverse map
+//     inv[row*K + slot] = position (or -1 when the slot is empty or the row is not valid);
+//   * the token tiles (expert, first entry, entry count <= block_m) the grouped GEMMs iterate over;
+//   * the plan words: tile count, K-split factors for both GEMMs, entry count.
+// It first waits (bounded) for every source rank's dispatch flag of this forward, so the receive
+// buffer is complete when it is read, and clears the split-K arrival counters.
+//
+// The stable expert-major order is a counting sort: every warp owns a contiguous range of the flat
+// (row, slot) index space, counts its keys per expert, a scan over (expert, warp) turns the counts
+// into start positions, and a second sweep places the entries.  No atomics, so the layout is the
+// same on every run.
+//
+// Replaces moeflow/kernels/metadata.py:24-137 (single-CTA Triton sort), the torch
+// sort/scatter_add/cumsum chain in moeflow/fixed.py:179-186 and build_tile_schedule
+// (moeflow/kernels/grouped_gemm.py:83-98).
+#include "common.cuh"
+#include "moeflow_b200.h"
+
+namespace mf {
+
+constexpr int kMetaThreads = 1024;
+constexpr int kMetaWarps = kMetaThreads / 32;
+
+// Exclusive scan of one int per thread over the whole block; `total` gets the sum.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += o;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < kMetaWarps ? warp_sums[lane] : 0;
+    int wi = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, wi, off);
+      if (lane >= off) wi += o;
+    }
+    warp_sums[lane] = wi - w;            // exclusive prefix of the warp sums
+    if (lane == 31) warp_sums[32] = wi;  // grand total
+  }
+  __syncthreads();
+  const int res = warp_sums[warp] + incl - v;
+  total = warp_sums[32];
+  __syncthreads();
+  return res;
+}
+
+// Pick the K split S in {1,2,4,8}: minimise waves(units*S) / S, prefer the smaller S on ties.
+__device__ __forceinline__ int choose_split(int units, int k_blocks, int n_sms, int max_slots) {
+  if (units <= 0) return 1;
+  int best = 1;
+  long long best_cost = (long long)((units + n_sms - 1) / n_sms) * 8;
+  for (int s = 2; s <= 8; s <<= 1) {
+    if (k_blocks % s != 0 || k_blocks / s < 2) break;
+    if ((long long)units * s > max_slots) break;
+    const long long cost = (long long)((units * s + n_sms - 1) / n_sms) * (8 / s);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+__global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta_args a) {
+  extern __shared__ int sm[];
+  const int L = a.L, K = a.K;
+  int* hist = sm;                       // [kMetaWarps][L]
+  int* cnt = hist + kMetaWarps * L;     // [L]
+  int* offs = cnt + L;                  // [L]
+  int* warp_sums = offs + L;            // [33]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned epoch = a.epoch ? *a.epoch : 0u;
+
+  if (a.flags != nullptr && tid < a.R) {
+    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kDispatchFlagTimeout, tid, 0, epoch);
+  }
+  for (int i = tid; i < a.n_counters1; i += kMetaThreads) a.counters1[i] = 0;
+  for (int i = tid; i < a.n_counters2; i += kMetaThreads) a.counters2[i] = 0;
+  for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
+  __syncthreads();
+
+  const int N = a.rows * K;
+  int per = (N + kMetaWarps - 1) / kMetaWarps;
+  per = (per + 31) & ~31;
+  const int begin = min(N, warp * per), end = min(N, (warp + 1) * per);
+  const uint8_t* recv = static_cast<const uint8_t*>(a.recv);
+  const size_t meta_off = (size_t)a.H * 2;
+  int* my_hist = hist + warp * L;
+
+  // sweep 1: per-warp histogram
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int key = -1;
+    if (i < end) {
+      const int row = i / K, slot = i - row * K;
+      const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
+      const int id = meta[slot];
+      if (meta[2 * K] != 0 && id >= 0 && id < L) key = id;
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (key >= 0 && lane == __ffs(same) - 1) my_hist[key] += __popc(same);
+    __syncwarp();
+  }
+  __syncthreads();
+
+  // per expert: prefix over warps, total count
+  for (int e = tid; e < L; e += kMetaThreads) {
+    int run = 0;
+    for (int w = 0; w < kMetaWarps; ++w) {
+      const int c = hist[w * L + e];
+      hist[w * L + e] = run;
+      run += c;
+    }
+    cnt[e] = run;
+  }
+  __syncthreads();
+
+  // scans over experts (L <= 1024: one expert per thread): entry offsets and tile bases
+  const int my_cnt = tid < L ? cnt[tid] : 0;
+  int n_entries, n_tiles;
+  const int my_off = block_exclusive_scan(my_cnt, warp_sums, n_entries);
+  const int my_nt = (my_cnt + a.block_m - 1) / a.block_m;
+  const int my_tb = block_exclusive_scan(my_nt, warp_sums, n_tiles);
+  if (tid < L) {
+    offs[tid] = my_off;
+    a.offsets[tid] = my_off;
+    for (int j = 0; j < my_nt; ++j) {
+      const int idx = my_tb + j;
+      if (idx < a.max_tiles) {
+        a.tile_e[idx] = tid;
+        a.tile_s[idx] = my_off + j * a.block_m;
+        a.tile_n[idx] = min(a.block_m, my_cnt - j * a.block_m);
+      }
+    }
+  }
+  if (tid == 0) {
+    a.offsets[L] = n_entries;
+    const int nt = min(n_tiles, a.max_tiles);
+    a.plan[MF_PLAN_N_TILES] = nt;
+    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, a.max_split_slots);
+    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, a.max_split_slots);
+    a.plan[MF_PLAN_N_ENTRIES] = n_entries;
+  }
+  __syncthreads();
+
+  // sweep 2: place the entries
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int key = -1, row = 0, slot = 0, wbits = 0;
+    if (i < end) {
+      row = i / K;
+      slot = i - row * K;
+      const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
+      const int id = meta[slot];
+      if (meta[2 * K] != 0 && id >= 0 && id < L) {
+        key = id;
+        wbits = meta[K + slot];
+      }
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (key >= 0) {
+      const int pos = offs[key] + my_hist[key] + __popc(same & ((1u << lane) - 1u));
+      a.entry_row[pos] = row;
+      a.entry_slot[pos] = slot;
+      a.entry_w[pos] = __int_as_float(wbits);
+      a.inv[i] = pos;
+    } else if (i < end) {
+      a.inv[i] = -1;
+    }
+    __syncwarp();
+    if (key >= 0 && lane == __ffs(same) - 1) my_hist[key] += __popc(same);
+    __syncwarp();
+  }
+}
+
+}  // namespace mf
+
+extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
+  if (!a || a->L < 1 || a->L > mf::kMetaThreads || a->R > mf::kMetaThreads || a->block_m < 1) return -1;
+  const size_t smem = ((size_t)mf::kMetaWarps * a->L + 2 * (size_t)a->L + 40) * sizeof(int);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(mf::expert_meta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  mf::expert_meta_kernel<<<1, mf::kMetaThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,456 @@
+// Grouped expert GEMMs on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+// The expert GEMMs of a decode step are weight-streaming bound: a few (1..64) token rows per expert
+// against tens of MB of expert weights.  The kernels below are therefore written "swap-AB": the
+// 128 weight rows of a block are the UMMA M dimension, the token rows are the UMMA N dimension
+// (16..n_max), accumulators live in tensor memory, and the weight stream is a deep TMA pipeline.
+//
+//   gate/up  : acc_gate[128, n] = W13[e, mb*128 + r, :] . X[n, :]     (and acc_up for rows I + ...)
+//              out[entry, mb*128 + r] = bf16( silu(min(gate, lim)) * clamp(up, +-lim) )
+//   down     : acc[128, n] = W2[e, mb*128 + r, :] . ACT[n, :]
+//              out[entry, mb*128 + r] = bf16( row_scale[entry] * acc )
+//
+// Work units are (token tile, 128-row weight block, K split).  The token tiles and the K split come
+// from a device-side plan (see expert_meta.cu), so nothing is read back to the host.  With a K split
+// S > 1 every unit stores its fp32 partial sums and the last unit to arrive (per 32-row quarter)
+// adds the S partials in split order 0..S-1, so the result does not depend on arrival order.
+//
+// Warp roles (256 threads, one CTA per SM, persistent over units blockIdx.x, +gridDim.x, ...):
+//   warp 0      TMA producer for the weight tiles (lane 0 issues)
+//   warp 1      UMMA issuer (lane 0 issues); owns the tensor-memory allocation
+//   warps 2-3   token-operand producers: gather rows by index with cp.async into the swizzled tile
+//   warps 4-7   epilogue: tcgen05.ld -> registers -> activation / scale -> global
+//
+// Replaces the reference's Triton grouped GEMM, unfused SwiGLU and expert-input gather
+// (moeflow/kernels/grouped_gemm.py:15-80, moeflow/experts.py:10-17, moeflow/kernels/expert_prepare.py:10-38).
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "moeflow_b200.h"
+
+namespace mf {
+
+constexpr int kBlockM = 128;          // weight rows per block (UMMA M)
+constexpr int kTileBytesA = 128 * 128;  // 128 rows x 128 bytes
+constexpr int kThreads = 256;
+constexpr int kGatherThreads = 64;
+constexpr int kAccStages = 2;
+
+template <bool kGateUp, int N_MAX>
+struct GemmCfg {
+  static constexpr int kATiles = kGateUp ? 2 : 1;
+  static constexpr int kStageA = kATiles * kTileBytesA;
+  static constexpr int kStageB = N_MAX * 128;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  // keep the pipeline under ~200 KB of the 227 KB a CTA may use
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kAccCols = kATiles * N_MAX;
+  static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128}
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct PipeState {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int n_stages) {
+    if (++stage == n_stages) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+template <bool kGateUp, int N_MAX>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_args a) {
+  using Cfg = GemmCfg<kGateUp, N_MAX>;
+  constexpr int STAGES = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;                                 // STAGES x kStageA
+  uint8_t* sB = smem + STAGES * Cfg::kStageA;         // STAGES x kStageB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;                          // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;                // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;             // [kAccStages]
+  uint64_t* acc_empty = acc_full + kAccStages;        // [kAccStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1 + kGatherThreads);  // TMA expect_tx arrive + one per gather thread
+      mbar_init(&empty_bar[s], 1);                  // tcgen05.commit
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      mbar_init(&acc_full[s], 1);   // tcgen05.commit
+      mbar_init(&acc_empty[s], 4);  // one per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_tiles = a.plan[MF_PLAN_N_TILES];
+  int split = a.plan[a.split_word];
+  if (split < 1) split = 1;
+  const int kb_per = a.k_blocks / split;
+  const int total_units = n_tiles * a.m_blocks * split;
+  const unsigned long long wait_ns = a.wait_ns;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ weight TMA producer
+    PipeState st;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int ks = u % split;
+      const int mb = (u / split) % a.m_blocks;
+      const int tt = u / (split * a.m_blocks);
+      const int e = a.tile_e[tt];
+      const int row0 = e * a.rows_per_expert + mb * kBlockM;
+      for (int j = 0; j < kb_per; ++j) {
+        const int kb = ks * kb_per + j;
+        ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 0, blockIdx.x, 0);
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageA);
+          uint8_t* dst = sA + st.stage * Cfg::kStageA;
+          tma_load_2d(dst, &tmap_w, &full_bar[st.stage], kb * 64, row0);
+          if (kGateUp) tma_load_2d(dst + kTileBytesA, &tmap_w, &full_bar[st.stage], kb * 64, row0 + a.up_row_offset);
+        }
+        __syncwarp();
+        st.advance(STAGES);
+      }
+    }
+    if (!ok) {
+      // Give copies that are still in flight a moment to land before the CTA goes away.
+      const unsigned long long t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 100000ull) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    PipeState st, acc;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt];
+      const uint32_t n_tile = (uint32_t)((n_rows + 15) & ~15);
+      const uint32_t idesc = umma_idesc(1, 1, kBlockM, n_tile < 16 ? 16 : n_tile);
+      ok = mbar_wait_bounded(&acc_empty[acc.stage], acc.phase ^ 1u, abort_flag, wait_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(a.status, kGemmAccTimeout, 1, blockIdx.x, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d0 = tmem_base + acc.stage * Cfg::kAccCols;
+      for (int j = 0; j < kb_per; ++j) {
+        ok = mbar_wait_bounded(&full_bar[st.stage], st.phase, abort_flag, wait_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmFullTimeout, 1, blockIdx.x, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          const uint32_t a_addr = smem_u32(sA + st.stage * Cfg::kStageA);
+          const uint32_t b_addr = smem_u32(sB + st.stage * Cfg::kStageB);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t bdesc = umma_desc_sw128(b_addr + k * 32);
+            const uint32_t accum = (j > 0 || k > 0) ? 1u : 0u;
+            umma_f16(d0, umma_desc_sw128(a_addr + k * 32), bdesc, idesc, accum);
+            if (kGateUp) umma_f16(d0 + N_MAX, umma_desc_sw128(a_addr + kTileBytesA + k * 32), bdesc, idesc, accum);
+          }
+          umma_commit(&empty_bar[st.stage]);
+        }
+        __syncwarp();
+        st.advance(STAGES);
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(&acc_full[acc.stage]);
+      __syncwarp();
+      acc.advance(kAccStages);
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ token-operand producers
+    const int gt = tid - 64;       // 0..63
+    const int r_in = gt >> 3;      // row inside an 8-row group == swizzle phase
+    const int chunk = gt & 7;      // 16-byte chunk inside the 128-byte row
+    const uint32_t sw_off = (uint32_t)((chunk ^ r_in) << 4);
+    PipeState st;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int ks = u % split;
+      const int tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt];
+      const int row_start = a.tile_s[tt];
+      int n_tile = (n_rows + 15) & ~15;
+      if (n_tile < 16) n_tile = 16;
+      const uint8_t* rp[N_MAX / 8];
+#pragma unroll
+      for (int i = 0; i < N_MAX / 8; ++i) {
+        const int n = r_in + 8 * i;
+        rp[i] = nullptr;
+        if (n < n_rows) {
+          const long long idx = a.b_index ? (long long)a.b_index[row_start + n] : (long long)(row_start + n);
+          rp[i] = static_cast<const uint8_t*>(a.b_base) + idx * a.b_pitch + chunk * 16;
+        }
+      }
+      for (int j = 0; j < kb_per; ++j) {
+        const int kb = ks * kb_per + j;
+        ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 2, blockIdx.x, 0);
+          break;
+        }
+        const uint32_t b_stage = smem_u32(sB + st.stage * Cfg::kStageB);
+#pragma unroll
+        for (int i = 0; i < N_MAX / 8; ++i) {
+          const int n = r_in + 8 * i;
+          if (n < n_tile) {
+            const bool live = rp[i] != nullptr;
+            cp_async_16(b_stage + n * 128 + sw_off, live ? (const void*)(rp[i] + (long long)kb * 128) : a.b_base,
+                        live ? 16u : 0u);
+          }
+        }
+        cp_async_mbar_arrive_noinc(&full_bar[st.stage]);
+        st.advance(STAGES);
+      }
+    }
+    // Drain this thread's cp.async operations before the CTA may exit.
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int wq = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = wq * 32 + lane;          // weight row inside the block
+    PipeState acc;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int ks = u % split;
+      const int mb = (u / split) % a.m_blocks;
+      const int tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt];
+      const int row_start = a.tile_s[tt];
+      int n_tile = (n_rows + 15) & ~15;
+      if (n_tile < 16) n_tile = 16;
+      ok = mbar_wait_bounded(&acc_full[acc.stage], acc.phase, abort_flag, wait_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + acc.stage * Cfg::kAccCols;
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
+      const long long out_col = (long long)mb * kBlockM + row;
+
+      if (split == 1) {
+        for (int c0 = 0; c0 < n_tile; c0 += 16) {
+          uint32_t g[16], up[16];
+          tmem_ld_16(taddr + c0, g);
+          if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = c0 + j;
+            if (n < n_rows) {
+              float v = __uint_as_float(g[j]);
+              if (kGateUp) {
+                float w = __uint_as_float(up[j]);
+                if (a.round_h) {
+                  v = bf16_round(v);
+                  w = bf16_round(w);
+                }
+                v = swiglu_clamped(v, w, a.limit);
+              } else if (a.row_scale) {
+                v *= a.row_scale[row_start + n];
+              }
+              out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
+      } else {
+        // Split K: park the fp32 partial sums, then the last quarter-warp to arrive reduces them.
+        const int tile_mb = tt * a.m_blocks + mb;
+        const long long slot_floats = (long long)Cfg::kATiles * N_MAX * kBlockM;
+        float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
+        for (int c0 = 0; c0 < n_tile; c0 += 16) {
+          uint32_t g[16], up[16];
+          tmem_ld_16(taddr + c0, g);
+          if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = c0 + j;
+            if (n < n_rows) {
+              __stcg(&mine[(long long)n * kBlockM + row], __uint_as_float(g[j]));
+              if (kGateUp) __stcg(&mine[(long long)(N_MAX + n) * kBlockM + row], __uint_as_float(up[j]));
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(&a.counters[tile_mb * 4 + wq], 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == split - 1) {
+          __threadfence();
+          const float* base = a.partial + (long long)tile_mb * split * slot_floats;
+          for (int n = 0; n < n_rows; ++n) {
+            float v = 0.f, w = 0.f;
+            for (int s = 0; s < split; ++s) {
+              const float* p = base + s * slot_floats;
+              v += __ldcg(&p[(long long)n * kBlockM + row]);
+              if (kGateUp) w += __ldcg(&p[(long long)(N_MAX + n) * kBlockM + row]);
+            }
+            if (kGateUp) {
+              if (a.round_h) {
+                v = bf16_round(v);
+                w = bf16_round(w);
+              }
+              v = swiglu_clamped(v, w, a.limit);
+            } else if (a.row_scale) {
+              v *= a.row_scale[row_start + n];
+            }
+            out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+          }
+          if (lane == 0) a.counters[tile_mb * 4 + wq] = 0;
+        }
+      }
+      acc.advance(kAccStages);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// -------------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+template <bool kGateUp, int N_MAX>
+static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<kGateUp, N_MAX>;
+  static bool configured = false;
+  auto kern = grouped_gemm_kernel<kGateUp, N_MAX>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap tm;
+  memcpy(&tm, tmap, sizeof(tm));
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm, *args);
+  return (int)cudaGetLastError();
+}
+
+static int check_args(const mf_gemm_args* a, int n_max, int grid) {
+  if (!a || grid < 1) return -1;
+  if (n_max != 32 && n_max != 64 && n_max != 128) return -2;
+  if (a->m_blocks < 1 || a->k_blocks < 1) return -3;
+  if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
+  return 0;
+}
+
+}  // namespace mf
+
+extern "C" {
+
+int mf_make_weight_tmap(void* out_tmap, const void* w, long long rows, long long k_elems, int elem_bytes) {
+  auto fn = mf::get_encode_fn();
+  if (!fn) return -10;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || ((k_elems * elem_bytes) & 15) != 0) return -11;
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(k_elems * elem_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(&tm, dt, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -12 - (int)r * 100;
+  memcpy(out_tmap, &tm, sizeof(tm));
+  return 0;
+}
+
+int mf_gemm_smem_bytes(int gate_up, int n_max) {
+  if (gate_up) {
+    if (n_max == 32) return mf::GemmCfg<true, 32>::kSmemBytes;
+    if (n_max == 64) return mf::GemmCfg<true, 64>::kSmemBytes;
+    if (n_max == 128) return mf::GemmCfg<true, 128>::kSmemBytes;
+  } else {
+    if (n_max == 32) return mf::GemmCfg<false, 32>::kSmemBytes;
+    if (n_max == 64) return mf::GemmCfg<false, 64>::kSmemBytes;
+    if (n_max == 128) return mf::GemmCfg<false, 128>::kSmemBytes;
+  }
+  return -1;
+}
+
+int mf_gemm_gate_up(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
+  int c = mf::check_args(args, n_max, grid);
+  if (c) return c;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_max == 32) return mf::launch<true, 32>(tmap, args, grid, s);
+  if (n_max == 64) return mf::launch<true, 64>(tmap, args, grid, s);
+  return mf::launch<true, 128>(tmap, args, grid, s);
+}
+
+int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
+  int c = mf::check_args(args, n_max, grid);
+  if (c) return c;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_max == 32) return mf::launch<false, 32>(tmap, args, grid, s);
+  if (n_max == 64) return mf::launch<false, 64>(tmap, args, grid, s);
+  return mf::launch<false, 128>(tmap, args, grid, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,164 @@
+// C ABI of libmoeflow_b200: every kernel launcher and runtime call the Python layer uses.
+// All launchers are asynchronous on the given stream, allocate nothing, and return a cudaError_t
+// value (0 = success) or a negative library error for bad arguments.
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* mf_stream_t;
+
+// ---- plan words written by mf_expert_meta and read by the grouped GEMMs -------------------------
+enum {
+  MF_PLAN_N_TILES = 0,    // number of (expert, row range) token tiles
+  MF_PLAN_SPLIT1 = 1,     // K split of the gate/up GEMM
+  MF_PLAN_SPLIT2 = 2,     // K split of the down GEMM
+  MF_PLAN_N_ENTRIES = 3,  // valid (row, slot) entries = offsets[L]
+  MF_PLAN_WORDS = 8
+};
+
+// ---- grouped GEMM -------------------------------------------------------------------------------
+typedef struct {
+  const void* b_base;        // token-side operand, rows of K elements (bf16) or K bytes (e4m3)
+  long long b_pitch;         // bytes between rows of b_base
+  const int* b_index;        // optional: entry -> row of b_base (gather); NULL = identity
+  const int* tile_e;         // per tile: local expert
+  const int* tile_s;         // per tile: first entry
+  const int* tile_n;         // per tile: number of entries (<= n_max)
+  const int* plan;           // MF_PLAN_* words
+  int split_word;            // MF_PLAN_SPLIT1 or MF_PLAN_SPLIT2
+  int m_blocks;              // 128-row weight blocks per expert
+  int k_blocks;              // K / 64 (bf16) or K / 128 (e4m3)
+  int rows_per_expert;       // weight rows per expert in the tensor map
+  int up_row_offset;         // gate/up only: row distance from a gate row to its up row
+  void* out;                 // bf16 [entries, out_pitch]
+  long long out_pitch;       // elements
+  const float* row_scale;    // down only, optional: per-entry multiplier applied to the fp32 sum
+  float* partial;            // split-K scratch, fp32
+  int* counters;             // split-K arrival counters (zero between launches)
+  int max_split_slots;       // capacity of `partial` in (tile, m-block, split) slots
+  float limit;               // SwiGLU clamp (<= 0: none)
+  int round_h;               // gate/up only: round gate and up to bf16 before the activation
+  unsigned long long* status;
+  unsigned long long wait_ns;
+  // block-scaled e4m3 only
+  const float* w_scale;      // [experts, rows_per_expert/128, K/128] fp32 (weight_scale_inv)
+  const float* b_scale;      // [b rows, K/128] fp32 activation scales (1x128 groups)
+  long long b_scale_pitch;   // floats between rows of b_scale
+  float* out_scale;          // gate/up fp8 output: [entries, I/128] scales of the quantised activation
+} mf_gemm_args;
+
+// Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
+// 128 rows with the 128-byte swizzle.  `out_tmap` receives 128 bytes.
+int mf_make_weight_tmap(void* out_tmap, const void* w, long long rows, long long k_elems, int elem_bytes);
+
+int mf_gemm_gate_up(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);
+int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);
+int mf_gemm_smem_bytes(int gate_up, int n_max);
+
+// ---- router / norm --------------------------------------------------------------------------------
+int mf_router_topk(const float* logits, const float* bias, float* weights, int* ids, int tokens, int experts,
+                   int top_k, int n_group, int topk_group, int sigmoid, int renorm, float scale,
+                   mf_stream_t stream);
+int mf_rmsnorm(const void* x, const void* gamma, void* out, int rows, int hidden, float eps, mf_stream_t stream);
+
+// ---- dispatch (pack + peer stores + flags) ----------------------------------------------------------
+typedef struct {
+  const void* x;             // [T, H] bf16
+  const float* weights;      // [T, K] fp32
+  const int* ids;            // [T, K] int32 global expert ids
+  const int* num_valid;      // optional device scalar: rows >= *num_valid are padding
+  const unsigned long long* peer_recv;  // [R] base addresses of every rank's recv buffer
+  const unsigned long long* peer_flag;  // [R] base addresses of every rank's dispatch flags [R]
+  unsigned char* hit;        // [C, R] local
+  unsigned* epoch;           // device-resident forward counter of this layer
+  unsigned* done_counter;    // zero between launches
+  int T, C, H, K, R, L, rank;
+  long long pitch;           // bytes per recv row
+  int skip_payload;          // 1: hidden lanes are stored only on rows with valid = 1
+} mf_dispatch_args;
+int mf_dispatch_push(const mf_dispatch_args* args, mf_stream_t stream);
+
+// ---- expert metadata ------------------------------------------------------------------------------------
+typedef struct {
+  const void* recv;          // [R*C rows] local receive buffer
+  long long pitch;           // bytes per row
+  int H, K, L, rows;         // rows = R*C
+  int R;
+  const unsigned* flags;     // [R] dispatch flags (local), may be NULL (no wait)
+  const unsigned* epoch;     // expected flag value
+  int* offsets;              // [L+1]
+  int* entry_row;            // [rows*K]
+  int* entry_slot;           // [rows*K]
+  float* entry_w;            // [rows*K]
+  int* inv;                  // [rows*K]
+  int* tile_e;               // [max_tiles]
+  int* tile_s;
+  int* tile_n;
+  int* plan;                 // MF_PLAN_WORDS
+  int* counters1;            // split-K counters to clear
+  int n_counters1;
+  int* counters2;
+  int n_counters2;
+  int block_m;               // tokens per tile (= n_max of the GEMMs)
+  int max_tiles;
+  int m_blocks1, k_blocks1, m_blocks2, k_blocks2;
+  int n_sms;
+  int max_split_slots;
+  unsigned long long* status;
+  unsigned long long wait_ns;
+} mf_meta_args;
+int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
+
+// ---- owner reduce + return push, combine -------------------------------------------------------------
+typedef struct {
+  const void* y;             // [entries, H] bf16 weighted expert outputs
+  const int* inv;            // [rows*K]
+  const void* recv;          // local receive buffer (valid flags)
+  long long pitch;
+  const unsigned long long* peer_ret;   // [R] base addresses of every rank's ret_recv [R, C, H]
+  const unsigned long long* peer_flag;  // [R] base addresses of every rank's return flags [R]
+  const unsigned* epoch;
+  unsigned* done_counter;
+  int R, C, H, K, rank;
+  int valid_word;            // index of the valid flag among a row's int32 metadata words (2 * top_k)
+} mf_reduce_push_args;
+int mf_owner_reduce_push(const mf_reduce_push_args* args, mf_stream_t stream);
+
+typedef struct {
+  const void* ret;           // local ret_recv [R, C, H] bf16
+  const unsigned char* hit;  // [C, R]
+  void* out;                 // [C, H] bf16
+  const unsigned* flags;     // [R] return flags (local), may be NULL
+  const unsigned* epoch;
+  int R, C, H, rank;
+  int ring;                  // 1: order (rank+1 .. rank+R) % R with bf16 rounding after every add
+  unsigned long long* status;
+  unsigned long long wait_ns;
+} mf_combine_args;
+int mf_combine(const mf_combine_args* args, mf_stream_t stream);
+
+// ---- activation quantisation (1x128 groups -> e4m3 + fp32 scales) --------------------------------------
+int mf_quant_rows_1x128(const void* x, long long x_pitch, const int* row_index, int rows, int hidden, void* q,
+                        float* scales, mf_stream_t stream);
+
+// ---- peer-memory runtime ------------------------------------------------------------------------------------
+int mf_peer_alloc(void** ptr, unsigned long long bytes);
+int mf_peer_free(void* ptr);
+int mf_peer_export(void* ptr, void* handle64);
+int mf_peer_open(const void* handle64, void** ptr);
+int mf_peer_close(void* ptr);
+int mf_peer_can_access(int dev, int peer_dev, int* ok);
+// Ping: store `value` into every peer's word [rank] then wait (bounded) until the local words all
+// reach `value`; `skip_store` leaves the stores out so that the wait runs out (status test).
+int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, int R, int rank, unsigned value,
+                 int skip_store, unsigned long long* status, unsigned long long wait_ns, mf_stream_t stream);
+const char* mf_error_string(int code);
+int mf_device_sm_count(int* out);
+
+#ifdef __cplusplus
+}
+#endif

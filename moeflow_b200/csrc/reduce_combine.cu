@@ -1,0 +1,145 @@
+// Owner-side reduce fused with the return all-to-all, and the source-side combine.
+//
+// owner_reduce_push: for every received row (s, t) that is valid,
+//     partial = bf16( sum_{k = 0..K-1, inv[row*K+k] >= 0} fp32(y[inv[row*K+k]]) )        (+0.0 start)
+// is stored straight into the source rank's combine buffer ret_recv_s[this rank, t] through the peer
+// mapping; the last CTA then publishes the epoch in every source's return flag [this rank].
+// `y` already holds bf16(routing weight * fp32 accumulator) from the down GEMM.
+//
+// combine: waits (bounded) for the return flags of all R owners, then
+//     out[t] = bf16( sum_{d = 0..R-1, hit[t, d]} fp32(ret[d, t]) )                        (+0.0 start)
+// in ascending owner order; rows without any hit are written as zeros.  The optional "ring" order
+// starts at the owner after this rank and rounds to bf16 after every add, which reproduces a bf16
+// ring reduce-scatter.
+//
+// Replaces moeflow/kernels/reduce.py:16-81 and the return all_to_all_single (moeflow/fixed.py:237).
+#include "common.cuh"
+#include "moeflow_b200.h"
+
+namespace mf {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&acc)[8]) {
+  uint4 o;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  return o;
+}
+
+__global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf_reduce_push_args a) {
+  __shared__ int s_pos[32];
+  const int row = blockIdx.x;  // = s*C + t
+  const int s = row / a.C, t = row - s * a.C;
+  const int tid = threadIdx.x;
+  const int* meta = reinterpret_cast<const int*>(static_cast<const uint8_t*>(a.recv) + (size_t)row * a.pitch +
+                                                 (size_t)a.H * 2);
+  const bool valid = meta[a.valid_word] != 0;
+  if (valid) {
+    if (tid < a.K) s_pos[tid] = a.inv[(size_t)row * a.K + tid];
+    __syncthreads();
+    const int chunks = a.H / 8;
+    const uint4* y = static_cast<const uint4*>(a.y);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.peer_ret[s]) +
+                                          ((size_t)a.rank * a.C + t) * a.H * 2);
+    for (int c = tid; c < chunks; c += kRowThreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < a.K; ++k) {
+        const int p = s_pos[k];
+        if (p >= 0) acc_bf16x8(acc, __ldcg(&y[(size_t)p * chunks + c]));
+      }
+      dst[c] = pack_bf16x8(acc);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned done = atomicAdd(a.done_counter, 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence_system();
+      *a.done_counter = 0u;
+      const unsigned epoch = *a.epoch;
+      for (int d = 0; d < a.R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, epoch);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_args a) {
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  const unsigned epoch = a.epoch ? *a.epoch : 0u;
+  if (a.flags != nullptr && tid < a.R) {
+    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);
+  }
+  __syncthreads();
+  const int chunks = a.H / 8;
+  const uint4* ret = static_cast<const uint4*>(a.ret);
+  uint4* out = static_cast<uint4*>(a.out) + (size_t)t * chunks;
+  const unsigned char* hit = a.hit + (size_t)t * a.R;
+  for (int c = tid; c < chunks; c += kRowThreads) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (!a.ring) {
+      for (int d = 0; d < a.R; ++d)
+        if (hit[d]) acc_bf16x8(acc, __ldcg(&ret[((size_t)d * a.C + t) * chunks + c]));
+    } else {
+      for (int step = 1; step <= a.R; ++step) {
+        const int d = (a.rank + step) % a.R;
+        if (hit[d]) {
+          acc_bf16x8(acc, __ldcg(&ret[((size_t)d * a.C + t) * chunks + c]));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = bf16_round(acc[i]);
+        }
+      }
+    }
+    out[c] = pack_bf16x8(acc);
+  }
+}
+
+// Peer ping used by the runtime tests: store a value into every peer's word [rank], then wait
+// (bounded) for all local words.  With skip_store nothing is stored, so the wait runs out and the
+// status word receives kPingTimeout: the time-out path is exercised without hanging anything.
+__global__ void peer_ping_kernel(const unsigned long long* peer_words, unsigned* local_words, int R, int rank,
+                                 unsigned value, int skip_store, unsigned long long* status,
+                                 unsigned long long wait_ns) {
+  const int d = threadIdx.x;
+  if (d >= R) return;
+  if (!skip_store) st_release_sys_u32(reinterpret_cast<unsigned*>(peer_words[d]) + rank, value);
+  if (!wait_flag_ge(local_words + d, value, wait_ns)) report_status(status, kPingTimeout, d, 0, value);
+}
+
+}  // namespace mf
+
+extern "C" {
+
+int mf_owner_reduce_push(const mf_reduce_push_args* a, mf_stream_t stream) {
+  if (!a || a->K > 32 || a->H % 8 != 0 || a->R < 1 || a->C < 1) return -1;
+  mf::owner_reduce_push_kernel<<<a->R * a->C, mf::kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+int mf_combine(const mf_combine_args* a, mf_stream_t stream) {
+  if (!a || a->H % 8 != 0 || a->R < 1 || a->R > mf::kRowThreads || a->C < 1) return -1;
+  mf::combine_kernel<<<a->C, mf::kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, int R, int rank, unsigned value,
+                 int skip_store, unsigned long long* status, unsigned long long wait_ns, mf_stream_t stream) {
+  if (R < 1 || R > 64) return -1;
+  mf::peer_ping_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(peer_words, local_words, R, rank, value,
+                                                                         skip_store, status, wait_ns);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

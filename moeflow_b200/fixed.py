@@ -1,0 +1,642 @@
+"""Fixed-capacity, CUDA-graph-capturable expert-parallel MoE layer.
+
+Same contract as the variable-size pipeline (``ep_moe``) — one copy per (token, rank), slot-ordered
+fp32 owner reduce, ascending-rank fp32 combine — with static shapes and no device-to-host traffic:
+
+* Positions are fixed: token t of rank s bound for rank d always occupies ``send[d, t]`` which lands
+  in ``recv[s, t]`` on d; a valid flag says whether t really hits d.  No count exchange.
+* A row is ``[H hidden lanes | K int32 local ids | K fp32 weights | int32 valid]`` bit-packed into
+  lanes of the activation dtype; the row pitch is padded to a multiple of 16 bytes so that rows can be
+  moved with 16-byte vector stores and read by TMA.
+
+Two backends share this surface:
+
+``backend="cuda"`` (B200): five kernels per forward and no library collective.  ``dispatch_push``
+packs rows and stores them straight into the owners' ``recv`` buffers over peer memory, then publishes
+an epoch flag; ``expert_meta`` waits for the flags and builds expert offsets, the tile map and the
+K-split plan on the device; two tcgen05 grouped GEMMs (gate/up + SwiGLU, down + routing weight)
+stream the expert weights by TMA; ``owner_reduce_push`` sums each row's slots in order and stores the
+partial row straight into the source rank's ``ret_recv``; ``combine`` waits for the return flags and
+merges by ascending rank in fp32.
+
+``backend="torch"``: the same stages in plain PyTorch for any device and dtype, exchanging the static
+buffers with ``all_to_all_single`` (NCCL or gloo).  It is the CPU path and the twin the CUDA kernels are
+compared against.
+
+Public surface follows the reference's ``moeflow/fixed.py:35-279``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .config import MoEConfig
+from .experts import BatchedTorchExperts, TorchLoopExperts
+from .router import route
+
+STAGES = ("ROUTER", "DISPATCH", "A2A_FORWARD", "EXPERT", "A2A_RETURN", "COMBINE")
+
+_DEFAULT_WAIT_NS = 2_000_000_000
+
+
+def meta_lanes(top_k: int, itemsize: int = 2) -> int:
+    """Lanes of ``itemsize`` bytes needed for K int32 ids + K fp32 weights + one int32 valid flag."""
+    nbytes = 4 * (2 * top_k + 1)
+    return (nbytes + itemsize - 1) // itemsize
+
+
+def row_pitch_lanes(hidden: int, top_k: int, itemsize: int = 2) -> int:
+    """Row pitch in lanes: hidden + metadata lanes, rounded up so that the pitch is a multiple of 16 B."""
+    per16 = max(1, 16 // itemsize)
+    lanes = hidden + meta_lanes(top_k, itemsize)
+    return (lanes + per16 - 1) // per16 * per16
+
+
+def _ordered_masked_sum(values: torch.Tensor, present: torch.Tensor) -> torch.Tensor:
+    """fp32 sum over dim 1 in index order from +0.0, skipping absent terms. ``values [N,S,H]``."""
+    acc = torch.zeros(values.shape[0], values.shape[2], dtype=torch.float32, device=values.device)
+    for i in range(values.shape[1]):
+        acc = torch.where(present[:, i, None], acc + values[:, i].to(torch.float32), acc)
+    return acc
+
+
+class FixedEPLayer:
+    def __init__(
+        self,
+        cfg: MoEConfig,
+        rank: int,
+        world: int,
+        w13_local: torch.Tensor | None,
+        w2_local: torch.Tensor | None,
+        capacity: int,
+        group: dist.ProcessGroup | None = None,
+        gemm_kwargs: dict | None = None,
+        metadata_kernel: bool = False,
+        fused_reduce: bool = False,
+        fused_combine: bool = False,
+        device: torch.device | None = None,
+        fused_dispatch: bool = False,
+        *,
+        backend: str | None = None,
+        dtype: torch.dtype | None = None,
+        peer_region=None,
+        wait_ns: int = _DEFAULT_WAIT_NS,
+        combine_mode: str = "fp32",
+    ):
+        """``capacity`` C is the static per-rank token budget of this layer instance.
+
+        The four boolean switches keep the reference's names.  On the torch backend they are accepted
+        and select nothing (every stage is PyTorch).  On the cuda backend every stage is a fused
+        kernel regardless; they exist so that call sites written for the reference keep working.
+
+        ``peer_region`` (cuda backend) is a ``SymmetricRegion`` of ``peer_bytes(...)`` bytes; when it is
+        None the layer allocates one through ``PeerGroup.from_dist(group)``.
+        """
+        if fused_reduce and not metadata_kernel:
+            raise ValueError("fused_reduce consumes the inverse map produced by metadata_kernel")
+        if combine_mode not in ("fp32", "bf16_ring"):
+            raise ValueError(f"unknown combine mode {combine_mode!r}")
+        self.cfg, self.rank, self.world, self.C = cfg, rank, world, capacity
+        self.L = cfg.experts_per_rank(world)
+        self.K, self.H, self.I = cfg.top_k, cfg.hidden_size, cfg.moe_intermediate_size
+        self.w13, self.w2 = w13_local, w2_local
+        self.group = group
+        self.gemm_kwargs = dict(gemm_kwargs or {})
+        self.metadata_kernel, self.fused_reduce = metadata_kernel, fused_reduce
+        self.fused_combine, self.fused_dispatch = fused_combine, fused_dispatch
+        self.combine_mode = combine_mode
+        self.wait_ns = int(wait_ns)
+        if device is None:
+            if w13_local is None:
+                raise ValueError("device is required when no weights are given")
+            device = w13_local.device
+        self.device = torch.device(device)
+        if dtype is None:
+            dtype = w13_local.dtype if w13_local is not None else torch.bfloat16
+        self.dtype = dtype
+        if backend is None:
+            backend = "cuda" if (self.device.type == "cuda" and dtype == torch.bfloat16 and _cuda_ok(cfg)) else "torch"
+        if backend not in ("cuda", "torch"):
+            raise ValueError(f"unknown backend {backend!r}")
+        self.backend = backend
+
+        R, Cc, K, H = world, capacity, self.K, self.H
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        self.row_width = H + meta_lanes(K, itemsize)
+        self.pitch = row_pitch_lanes(H, K, itemsize)
+        self.n_entries = R * Cc * K
+        dev = self.device
+
+        if backend == "cuda":
+            self._init_cuda(peer_region)
+        else:
+            self._recv_store = torch.zeros(R, Cc, self.pitch, dtype=dtype, device=dev)
+            self.ret_recv = torch.zeros(R, Cc, H, dtype=dtype, device=dev)
+            self.out = torch.zeros(Cc, H, dtype=dtype, device=dev)
+        # Send-side staging exists only on the torch backend (the cuda backend stores into peers).
+        if backend == "torch":
+            self._send_store = torch.zeros(R, Cc, self.pitch, dtype=dtype, device=dev)
+            self.ret_send = torch.zeros(R, Cc, H, dtype=dtype, device=dev)
+            self.send = self._send_store[:, :, : self.row_width]
+        self.recv = self._recv_store[:, :, : self.row_width]
+        self._rank_ids = torch.arange(R, device=dev)
+        self._tok_ids = torch.arange(Cc, device=dev)
+        self.torch_experts = self.gemm_kwargs.get("torch_experts") or (
+            TorchLoopExperts() if dev.type == "cpu" else BatchedTorchExperts()
+        )
+
+    # ------------------------------------------------------------------------------------------
+    # views
+    # ------------------------------------------------------------------------------------------
+    def _meta_view(self, store: torch.Tensor) -> torch.Tensor:
+        """int32 view ``[R, C, 2K+1]`` of the metadata lanes of a row store."""
+        lanes = meta_lanes(self.K, store.element_size())
+        return store[:, :, self.H : self.H + lanes].view(torch.int32)[:, :, : 2 * self.K + 1]
+
+    @staticmethod
+    def peer_bytes(cfg: MoEConfig, world: int, capacity: int) -> int:
+        """Bytes of the symmetric region one cuda-backend layer needs."""
+        return _CudaLayout(cfg, world, capacity).total
+
+    # ------------------------------------------------------------------------------------------
+    # stage 1 (source): route and pack
+    # ------------------------------------------------------------------------------------------
+    def stage_route(self, logits: torch.Tensor, bias: torch.Tensor | None) -> tuple[torch.Tensor, torch.Tensor]:
+        """ROUTER: ``logits [T, E]`` -> ``(weights [T, K] fp32, ids [T, K])``."""
+        if self.backend == "cuda":
+            from .ops.kernels import router_topk
+
+            T = logits.shape[0]
+            return router_topk(logits, bias, self.cfg, self._route_w[:T], self._route_ids[:T])
+        weights, ids = route(logits, bias, self.cfg)
+        return weights, ids.to(torch.int64)
+
+    def stage_dispatch_pack(
+        self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, num_valid: torch.Tensor | None = None
+    ) -> torch.Tensor:
+        """DISPATCH: fill the rows this rank sends.  Rows ``t >= num_valid`` (device scalar) are padding.
+
+        Returns ``hit [C, R]``: token t has at least one expert on rank r.  On the cuda backend the rows
+        are stored directly into the owners' ``recv`` buffers (this stage *is* the forward all-to-all).
+        """
+        T = x.shape[0]
+        if T > self.C:
+            raise ValueError(f"{T} tokens exceed capacity {self.C}")
+        if self.backend == "cuda":
+            return self._cuda_dispatch(x, weights, ids, num_valid)
+        R, K, H, L = self.world, self.K, self.H, self.L
+        ids = ids.to(torch.int64)
+        owner = torch.div(ids, L, rounding_mode="floor")  # [T, K]
+        on = owner[:, None, :] == self._rank_ids[None, :, None]  # [T, R, K]
+        hit = on.any(dim=-1)
+        if num_valid is not None:
+            hit = hit & (self._tok_ids[:T] < num_valid)[:, None]
+        on = on & hit[:, :, None]
+        local = torch.where(on, ids[:, None, :] - self._rank_ids[None, :, None] * L, -1).to(torch.int32)
+        w = torch.where(on, weights.to(torch.float32)[:, None, :], 0.0)
+
+        self._send_store[:, :T, :H] = x.to(self.dtype)[None]
+        meta = self._meta_view(self._send_store)
+        meta[:, :T, :K] = local.permute(1, 0, 2)
+        meta[:, :T, K : 2 * K] = w.permute(1, 0, 2).contiguous().view(torch.int32)
+        meta[:, :T, 2 * K] = hit.transpose(0, 1).to(torch.int32)
+        if T < self.C:
+            meta[:, T:, :K] = -1
+            meta[:, T:, K:] = 0
+            hit = torch.cat([hit, hit.new_zeros(self.C - T, R)], dim=0)
+        return hit
+
+    def stage_pack(self, x, logits, bias, num_valid=None) -> torch.Tensor:
+        """ROUTER + DISPATCH. Returns ``hit [C, R]``."""
+        weights, ids = self.stage_route(logits, bias)
+        return self.stage_dispatch_pack(x, weights, ids, num_valid)
+
+    # ------------------------------------------------------------------------------------------
+    # stage 2 (owner): experts + slot-ordered reduce
+    # ------------------------------------------------------------------------------------------
+    def received_routing(self) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Unpack ``recv``: ``(hidden [RC, H], local ids [RC, K] (-1 = none), weights [RC, K] fp32)``."""
+        R, Cc, K, H = self.world, self.C, self.K, self.H
+        rows = self._recv_store.view(R * Cc, self.pitch)
+        meta = self._meta_view(self._recv_store).reshape(R * Cc, 2 * K + 1)
+        valid = meta[:, 2 * K] != 0
+        local = torch.where(valid[:, None], meta[:, :K].to(torch.int64), -1)
+        wts = meta[:, K : 2 * K].contiguous().view(torch.float32)
+        return rows[:, :H], local, wts
+
+    def stage_experts(self, expert_fn=None, prepare_fn=None, *, direct_output: bool = False) -> torch.Tensor | None:
+        """Consume ``recv [R(src), C, row]`` and produce one partial row per received row.
+
+        ``expert_fn(x_rows [RC, H], local_ids [RC, K] (-1 = no hit), weights [RC, K] fp32) -> [RC, H]``
+        replaces the built-in experts and owner reduce.  ``prepare_fn(rows [RC, row_width])`` may own
+        the received-row format and returns the argument tuple for ``expert_fn``.  With
+        ``direct_output`` the tensor ``expert_fn`` returns is itself used as the return buffer (no
+        copy) after a strict shape/dtype/device/contiguity check, and is returned as ``[R, C, H]``.
+        """
+        R, Cc, H = self.world, self.C, self.H
+        if direct_output and prepare_fn is None:
+            raise ValueError("Direct expert output requires custom input preparation")
+        if prepare_fn is not None:
+            if expert_fn is None:
+                raise ValueError("Custom input preparation requires an external expert function")
+            if self.backend == "cuda":
+                self._cuda_meta()  # waits for the dispatch flags of every source rank
+            rows = self._recv_store.view(R * Cc, self.pitch)[:, : self.row_width]
+            output = expert_fn(*prepare_fn(rows))
+            if direct_output:
+                if (
+                    tuple(output.shape) != (R * Cc, H)
+                    or output.dtype != self.dtype
+                    or output.device != self._recv_store.device
+                    or not output.is_contiguous()
+                ):
+                    raise ValueError("Direct expert output must be contiguous and match return shape, dtype and device")
+                return output.view(R, Cc, H)
+            self._store_partials(output)
+            return None
+        if expert_fn is not None:
+            if self.backend == "cuda":
+                self._cuda_meta()  # waits for the dispatch flags of every source rank
+            x_rows, local, wts = self.received_routing()
+            self._store_partials(expert_fn(x_rows, local, wts))
+            return None
+        if self.backend == "cuda":
+            self._cuda_experts()
+            return None
+        self._torch_experts()
+        return None
+
+    def _store_partials(self, partials: torch.Tensor) -> None:
+        """Partial rows ``[RC, H]`` -> the return path (staging buffer, or peers on the cuda backend)."""
+        if self.backend == "cuda":
+            self._cuda_push_partials(partials)
+        else:
+            self.ret_send.view(self.world * self.C, self.H).copy_(partials)
+
+    def _torch_layout(self, local: torch.Tensor):
+        """Stable expert-major order of the (row, slot) entries; sentinel L collects empty slots."""
+        L, K = self.L, self.K
+        keys = torch.where(local >= 0, local, L).reshape(-1)
+        order = torch.sort(keys, stable=True).indices
+        counts = torch.bincount(keys, minlength=L + 1)
+        offsets = torch.zeros(L + 1, dtype=torch.int64, device=keys.device)
+        torch.cumsum(counts[:L], dim=0, out=offsets[1:])
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=order.device)
+        inv = torch.where(keys < L, inv, -1)
+        return order, offsets, inv, torch.div(order, K, rounding_mode="floor"), order % K
+
+    def _torch_experts(self) -> None:
+        R, Cc, K, H = self.world, self.C, self.K, self.H
+        x_rows, local, wts = self.received_routing()
+        order, offsets, inv, entry_row, entry_slot = self._torch_layout(local)
+        n_live = offsets[-1]
+        if isinstance(self.torch_experts, TorchLoopExperts):
+            n = int(n_live)  # host read: the torch backend is not the graph-captured product path
+            rows = x_rows[entry_row[:n]]
+            y = self.torch_experts(rows, offsets, self.w13, self.w2, self.cfg.swiglu_limit, wts[entry_row[:n], entry_slot[:n]])
+            y = torch.cat([y, y.new_zeros(order.numel() - n + 1, H)], dim=0)
+        else:
+            rows = x_rows[entry_row]
+            y = self.torch_experts(rows, offsets, self.w13, self.w2, self.cfg.swiglu_limit, wts[entry_row, entry_slot])
+            y = torch.cat([y, y.new_zeros(1, H)], dim=0)
+        gathered = y[inv.view(R * Cc, K)]  # -1 picks the trailing zero row and is masked anyway
+        partial = _ordered_masked_sum(gathered, local >= 0)
+        self.ret_send.view(R * Cc, H).copy_(partial.to(self.dtype))
+
+    # ------------------------------------------------------------------------------------------
+    # stage 3 (source): combine
+    # ------------------------------------------------------------------------------------------
+    def stage_combine(self, hit: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        if self.backend == "cuda" and out_dtype == torch.bfloat16:
+            return self._cuda_combine(hit)
+        return combine_partials(self.ret_recv, hit, out_dtype, self.rank, self.combine_mode)
+
+    # ------------------------------------------------------------------------------------------
+    # exchanges (torch backend) and SPMD entry points
+    # ------------------------------------------------------------------------------------------
+    def _exchange(self, out: torch.Tensor, inp: torch.Tensor) -> None:
+        if self.world == 1 and (self.group is None or not dist.is_initialized()):
+            out.copy_(inp)
+            return
+        try:
+            dist.all_to_all_single(out, inp, group=self.group)
+        except RuntimeError:
+            outs = [t.contiguous() for t in out.unbind(0)]
+            dist.all_to_all(outs, [t.contiguous() for t in inp.unbind(0)], group=self.group)
+            for dst, src in zip(out.unbind(0), outs):
+                dst.copy_(src)
+
+    def forward_routed(
+        self,
+        x,
+        weights,
+        ids,
+        num_valid: torch.Tensor | None = None,
+        expert_fn=None,
+        combine_fn=None,
+        prepare_fn=None,
+        direct_expert_output: bool = False,
+    ):
+        """Pre-routed forward; ``combine_fn(ret_recv, hit)`` may replace the built-in combine."""
+        T = x.shape[0]
+        hit = self.stage_dispatch_pack(x, weights, ids, num_valid)
+        if self.backend == "torch":
+            self._exchange(self._recv_store, self._send_store)
+        partials = self.stage_experts(expert_fn, prepare_fn=prepare_fn, direct_output=direct_expert_output)
+        if self.backend == "torch":
+            self._exchange(self.ret_recv, self.ret_send if partials is None else partials)
+        elif partials is not None:
+            self._cuda_push_partials(partials.view(self.world * self.C, self.H))
+        if combine_fn is not None:
+            if self.backend == "cuda":
+                self._cuda_wait_return()
+            out = combine_fn(self.ret_recv, hit)
+        else:
+            out = self.stage_combine(hit, x.dtype)
+        return out[:T]
+
+    def forward(self, x, logits, bias, num_valid: torch.Tensor | None = None, stop_after: str | None = None):
+        """Whole layer; ``stop_after`` (one of ``STAGES``) truncates it for prefix-graph stage timing."""
+        if stop_after is not None and stop_after not in STAGES:
+            raise ValueError(f"stop_after must be one of {STAGES}")
+        weights, ids = self.stage_route(logits, bias)
+        if stop_after == "ROUTER":
+            return weights
+        hit = self.stage_dispatch_pack(x, weights, ids, num_valid)
+        if stop_after == "DISPATCH":
+            return hit
+        if self.backend == "torch":
+            self._exchange(self._recv_store, self._send_store)
+        if stop_after == "A2A_FORWARD":
+            return self.recv
+        self.stage_experts()
+        if stop_after == "EXPERT":
+            return self.ret_recv if self.backend == "cuda" else self.ret_send
+        if self.backend == "torch":
+            self._exchange(self.ret_recv, self.ret_send)
+        if stop_after == "A2A_RETURN":
+            return self.ret_recv
+        return self.stage_combine(hit, x.dtype)
+
+    # ------------------------------------------------------------------------------------------
+    # cuda backend
+    # ------------------------------------------------------------------------------------------
+    def _init_cuda(self, peer_region) -> None:
+        from .ops import _lib
+        from .ops.kernels import make_weight_tmap, sm_count
+        from .parallel.peer import PeerGroup
+
+        cfg, R, Cc, K, H, I, L = self.cfg, self.world, self.C, self.K, self.H, self.I, self.L
+        dev = self.device
+        if not _cuda_ok(cfg):
+            raise ValueError("cuda backend needs hidden and intermediate sizes that are multiples of 128")
+        lay = _CudaLayout(cfg, R, Cc)
+        self._layout = lay
+        if peer_region is None:
+            peer_region = PeerGroup(self.rank, R, self.group, dev).allocate(lay.total)
+        if peer_region.world != R or peer_region.local.nbytes < lay.total:
+            raise ValueError("peer region does not fit this layer")
+        self.peer_region = peer_region
+        self._recv_store = peer_region.view(lay.recv_off, (R, Cc, self.pitch), torch.bfloat16)
+        self.ret_recv = peer_region.view(lay.ret_off, (R, Cc, H), torch.bfloat16)
+        self._disp_flags = peer_region.view(lay.dflag_off, (R,), torch.int32)
+        self._ret_flags = peer_region.view(lay.rflag_off, (R,), torch.int32)
+        self._peer_recv = peer_region.table(lay.recv_off)
+        self._peer_ret = peer_region.table(lay.ret_off)
+        self._peer_dflag = peer_region.table(lay.dflag_off)
+        self._peer_rflag = peer_region.table(lay.rflag_off)
+
+        i32 = dict(dtype=torch.int32, device=dev)
+        N = self.n_entries
+        self.block_m = int(self.gemm_kwargs.get("block_m", 64))
+        if self.block_m not in (32, 64, 128):
+            raise ValueError("block_m must be 32, 64 or 128")
+        self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
+        self.max_tiles = (N + self.block_m - 1) // self.block_m + L
+        self.max_split_slots = 2 * self.n_sms
+        self.out = torch.zeros(Cc, H, dtype=torch.bfloat16, device=dev)
+        self.hit = torch.zeros(Cc, R, dtype=torch.uint8, device=dev)
+        self._route_w = torch.zeros(Cc, K, dtype=torch.float32, device=dev)
+        self._route_ids = torch.zeros(Cc, K, **i32)
+        self._epoch = torch.zeros(1, **i32)
+        self._done = torch.zeros(4, **i32)
+        self.status = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.offsets = torch.zeros(L + 1, **i32)
+        self.entry_row = torch.zeros(N, **i32)
+        self.entry_slot = torch.zeros(N, **i32)
+        self.entry_w = torch.zeros(N, dtype=torch.float32, device=dev)
+        self.inv = torch.zeros(N, **i32)
+        self.tile_e = torch.zeros(self.max_tiles, **i32)
+        self.tile_s = torch.zeros(self.max_tiles, **i32)
+        self.tile_n = torch.zeros(self.max_tiles, **i32)
+        self.plan = torch.zeros(_lib.PLAN_WORDS, **i32)
+        self.act = torch.zeros(N, I, dtype=torch.bfloat16, device=dev)
+        self.y = torch.zeros(N, H, dtype=torch.bfloat16, device=dev)
+        mb1, mb2 = I // 128, H // 128
+        self._counters1 = torch.zeros(self.max_tiles * mb1 * 4, **i32)
+        self._counters2 = torch.zeros(self.max_tiles * mb2 * 4, **i32)
+        self._partial = torch.zeros(self.max_split_slots * 2 * self.block_m * 128, dtype=torch.float32, device=dev)
+        self._keep: list = []  # ctypes objects and temporaries that must outlive launches
+
+        S = _lib
+        self._a_dispatch = S.DispatchArgs(
+            peer_recv=self._peer_recv.data_ptr(), peer_flag=self._peer_dflag.data_ptr(), hit=self.hit.data_ptr(),
+            epoch=self._epoch.data_ptr(), done_counter=self._done[0:].data_ptr(), T=0, C=Cc, H=H, K=K, R=R, L=L,
+            rank=self.rank, pitch=self.pitch * 2, skip_payload=int(self.gemm_kwargs.get("skip_payload", 1)),
+        )
+        self._a_meta = S.MetaArgs(
+            recv=self._recv_store.data_ptr(), pitch=self.pitch * 2, H=H, K=K, L=L, rows=R * Cc, R=R,
+            flags=self._disp_flags.data_ptr(), epoch=self._epoch.data_ptr(), offsets=self.offsets.data_ptr(),
+            entry_row=self.entry_row.data_ptr(), entry_slot=self.entry_slot.data_ptr(), entry_w=self.entry_w.data_ptr(),
+            inv=self.inv.data_ptr(), tile_e=self.tile_e.data_ptr(), tile_s=self.tile_s.data_ptr(),
+            tile_n=self.tile_n.data_ptr(), plan=self.plan.data_ptr(), counters1=self._counters1.data_ptr(),
+            n_counters1=self._counters1.numel(), counters2=self._counters2.data_ptr(),
+            n_counters2=self._counters2.numel(), block_m=self.block_m, max_tiles=self.max_tiles, m_blocks1=mb1,
+            k_blocks1=H // 64, m_blocks2=mb2, k_blocks2=I // 64, n_sms=self.n_sms,
+            max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
+        )
+        limit = cfg.swiglu_limit if cfg.swiglu_limit is not None else 0.0
+        common = dict(
+            tile_e=self.tile_e.data_ptr(), tile_s=self.tile_s.data_ptr(), tile_n=self.tile_n.data_ptr(),
+            plan=self.plan.data_ptr(), partial=self._partial.data_ptr(), max_split_slots=self.max_split_slots,
+            limit=float(limit), round_h=int(self.gemm_kwargs.get("round_h", 0)), status=self.status.data_ptr(),
+            wait_ns=self.wait_ns,
+        )
+        self._a_gemm1 = S.GemmArgs(
+            b_base=self._recv_store.data_ptr(), b_pitch=self.pitch * 2, b_index=self.entry_row.data_ptr(),
+            split_word=S.PLAN_SPLIT1, m_blocks=mb1, k_blocks=H // 64, rows_per_expert=2 * I, up_row_offset=I,
+            out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=self._counters1.data_ptr(), **common,
+        )
+        self._a_gemm2 = S.GemmArgs(
+            b_base=self.act.data_ptr(), b_pitch=I * 2, b_index=None, split_word=S.PLAN_SPLIT2, m_blocks=mb2,
+            k_blocks=I // 64, rows_per_expert=H, up_row_offset=0, out=self.y.data_ptr(), out_pitch=H,
+            row_scale=self.entry_w.data_ptr(), counters=self._counters2.data_ptr(), **common,
+        )
+        self._a_reduce = S.ReducePushArgs(
+            y=self.y.data_ptr(), inv=self.inv.data_ptr(), recv=self._recv_store.data_ptr(), pitch=self.pitch * 2,
+            peer_ret=self._peer_ret.data_ptr(), peer_flag=self._peer_rflag.data_ptr(), epoch=self._epoch.data_ptr(),
+            done_counter=self._done[1:].data_ptr(), R=R, C=Cc, H=H, K=K, rank=self.rank, valid_word=2 * K,
+        )
+        self._row_ids = torch.arange(R * Cc, **i32)
+        self._a_push = S.ReducePushArgs(
+            y=None, inv=self._row_ids.data_ptr(), recv=self._recv_store.data_ptr(), pitch=self.pitch * 2,
+            peer_ret=self._peer_ret.data_ptr(), peer_flag=self._peer_rflag.data_ptr(), epoch=self._epoch.data_ptr(),
+            done_counter=self._done[2:].data_ptr(), R=R, C=Cc, H=H, K=1, rank=self.rank, valid_word=2 * K,
+        )
+        self._scratch_out = None
+        self._a_combine = S.CombineArgs(
+            ret=self.ret_recv.data_ptr(), hit=self.hit.data_ptr(), out=self.out.data_ptr(),
+            flags=self._ret_flags.data_ptr(), epoch=self._epoch.data_ptr(), R=R, C=Cc, H=H, rank=self.rank,
+            ring=int(self.combine_mode == "bf16_ring"), status=self.status.data_ptr(), wait_ns=self.wait_ns,
+        )
+        self._tmap13 = self._tmap2 = None
+        if self.w13 is not None:
+            self.set_weights(self.w13, self.w2)
+        self._lib = _lib.lib()
+        self._make_tmap = make_weight_tmap
+
+    def set_weights(self, w13_local: torch.Tensor, w2_local: torch.Tensor) -> None:
+        """(Re)bind the local expert shard: ``w13 [L, 2I, H]``, ``w2 [L, H, I]`` bf16, contiguous."""
+        from .ops.kernels import make_weight_tmap
+
+        L, H, I = self.L, self.H, self.I
+        if tuple(w13_local.shape) != (L, 2 * I, H) or tuple(w2_local.shape) != (L, H, I):
+            raise ValueError("weight shard has the wrong shape")
+        if w13_local.dtype != torch.bfloat16 or w2_local.dtype != torch.bfloat16:
+            raise ValueError("cuda backend takes bf16 weights")
+        self.w13, self.w2 = w13_local.contiguous(), w2_local.contiguous()
+        self._tmap13 = make_weight_tmap(self.w13)
+        self._tmap2 = make_weight_tmap(self.w2)
+
+    def _cuda_dispatch(self, x, weights, ids, num_valid) -> torch.Tensor:
+        from .ops import _lib
+
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("x must be contiguous bf16")
+        if ids.dtype != torch.int32:
+            ids = ids.to(torch.int32)
+        weights = weights.to(torch.float32).contiguous()
+        ids = ids.contiguous()
+        a = self._a_dispatch
+        a.x, a.weights, a.ids = x.data_ptr(), weights.data_ptr(), ids.data_ptr()
+        a.num_valid = None if num_valid is None else num_valid.data_ptr()
+        a.T = x.shape[0]
+        self._keep = [x, weights, ids, num_valid]
+        _lib.check(self._lib.mf_dispatch_push(C.byref(a), _lib.stream_ptr()), "dispatch_push")
+        return self.hit
+
+    def _cuda_meta(self) -> None:
+        from .ops import _lib
+
+        _lib.check(self._lib.mf_expert_meta(C.byref(self._a_meta), _lib.stream_ptr()), "expert_meta")
+
+    def _cuda_experts(self) -> None:
+        from .ops import _lib
+
+        if self._tmap13 is None:
+            raise RuntimeError("no expert weights bound (set_weights)")
+        s = _lib.stream_ptr()
+        self._cuda_meta()
+        _lib.check(self._lib.mf_gemm_gate_up(self._tmap13, C.byref(self._a_gemm1), self.block_m, self.n_sms, s), "gate/up gemm")
+        _lib.check(self._lib.mf_gemm_down(self._tmap2, C.byref(self._a_gemm2), self.block_m, self.n_sms, s), "down gemm")
+        _lib.check(self._lib.mf_owner_reduce_push(C.byref(self._a_reduce), s), "owner_reduce_push")
+
+    def _cuda_push_partials(self, partials: torch.Tensor) -> None:
+        """Return path for externally computed partial rows ``[RC, H]``: peer stores + return flags."""
+        from .ops import _lib
+
+        if tuple(partials.shape) != (self.world * self.C, self.H) or partials.dtype != torch.bfloat16:
+            raise ValueError("partial rows must be bf16 [R*C, H]")
+        partials = partials.contiguous()
+        self._a_push.y = partials.data_ptr()
+        self._keep.append(partials)
+        _lib.check(self._lib.mf_owner_reduce_push(C.byref(self._a_push), _lib.stream_ptr()), "return push")
+
+    def _cuda_wait_return(self) -> None:
+        """Block the stream until every owner's return flag of this forward has arrived."""
+        self._cuda_combine(self.hit)
+
+    def _cuda_combine(self, hit: torch.Tensor) -> torch.Tensor:
+        from .ops import _lib
+
+        _lib.check(self._lib.mf_combine(C.byref(self._a_combine), _lib.stream_ptr()), "combine")
+        return self.out
+
+    def check_status(self) -> dict:
+        """Read the layer's status word (device-to-host; call it outside captured regions)."""
+        from .ops import _lib
+
+        if self.backend != "cuda":
+            return _lib.decode_status(0)
+        return _lib.decode_status(int(self.status.item()))
+
+
+class _CudaLayout:
+    """Offsets inside the symmetric region of one cuda-backend layer."""
+
+    def __init__(self, cfg: MoEConfig, world: int, capacity: int):
+        pitch_bytes = row_pitch_lanes(cfg.hidden_size, cfg.top_k, 2) * 2
+
+        def up(n: int, a: int = 1024) -> int:
+            return (n + a - 1) // a * a
+
+        self.recv_off = 0
+        self.ret_off = up(world * capacity * pitch_bytes)
+        self.dflag_off = self.ret_off + up(world * capacity * cfg.hidden_size * 2)
+        self.rflag_off = self.dflag_off + up(world * 4, 256)
+        self.total = self.rflag_off + up(world * 4, 256)
+
+
+def _cuda_ok(cfg: MoEConfig) -> bool:
+    from .ops import _lib
+
+    return (
+        cfg.hidden_size % 128 == 0 and cfg.moe_intermediate_size % 128 == 0 and cfg.top_k <= 32 and _lib.available()
+    )
+
+
+def combine_partials(ret_recv: torch.Tensor, hit: torch.Tensor, out_dtype, rank: int = 0, mode: str = "fp32"):
+    """Source-side merge of ``ret_recv [R, C, H]`` under ``hit [C, R]`` in PyTorch.
+
+    ``fp32``: ascending rank, fp32 accumulator from +0.0, one cast.  ``bf16_ring``: start at the rank
+    after ``rank`` and round to bf16 after every add (the arithmetic of a bf16 ring reduce-scatter).
+    """
+    R = ret_recv.shape[0]
+    present = hit.to(torch.bool)
+    if mode == "fp32":
+        return _ordered_masked_sum(ret_recv.permute(1, 0, 2), present).to(out_dtype)
+    acc = torch.zeros(ret_recv.shape[1], ret_recv.shape[2], dtype=torch.float32, device=ret_recv.device)
+    for step in range(1, R + 1):
+        d = (rank + step) % R
+        term = torch.where(present[:, d, None], ret_recv[d].to(torch.float32), 0.0)
+        acc = (acc + term).to(torch.bfloat16).to(torch.float32)
+    return acc.to(out_dtype)
+
+
+def simulate_fixed(layers: list[FixedEPLayer], xs, logits, bias, num_valid=None) -> list[torch.Tensor]:
+    """All ranks in lock-step inside one process.
+
+    Torch-backend layers exchange by copying ``recv[d][s] = send[s][d]``; cuda-backend layers built on
+    ``PeerGroup.local`` regions store into each other directly, so running the stages rank after rank
+    is the exchange (every flag is already published when its waiter runs).
+    """
+    R = len(layers)
+    hits = [
+        ly.stage_pack(x, lg, bias, None if num_valid is None else num_valid[i])
+        for i, (ly, x, lg) in enumerate(zip(layers, xs, logits))
+    ]
+    if layers[0].backend == "torch":
+        for d in range(R):
+            for s in range(R):
+                layers[d]._recv_store[s].copy_(layers[s]._send_store[d])
+    for ly in layers:
+        ly.stage_experts()
+    if layers[0].backend == "torch":
+        for d in range(R):
+            for s in range(R):
+                layers[d].ret_recv[s].copy_(layers[s].ret_send[d])
+    return [ly.stage_combine(h, x.dtype) for ly, h, x in zip(layers, hits, xs)]

@@ -1,0 +1,237 @@
+"""The cuda backend of FixedEPLayer, kernel by kernel and end to end, on one GPU.
+
+Several EP ranks are simulated inside one process: every "rank" owns a peer region on the same GPU
+and the ranks' kernels run one after another, so each flag is already published when its waiter
+runs (kernels that wait on one another never run concurrently here).
+"""
+
+import pytest
+import torch
+
+from conftest import SMALL_GPU, replace
+from moeflow_b200.ep_moe import EPMoELayer, shard_experts, simulate_ep
+from moeflow_b200.fixed import FixedEPLayer, simulate_fixed
+from moeflow_b200.reference import moe_reference
+from moeflow_b200.testing import make_bias, make_hidden, make_logits, make_weights
+from moeflow_b200.tolerances import bitwise_equal, gemm_tolerance, normwise_rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _layers(cfg, world, capacity, w13, w2, backend, **kw):
+    from moeflow_b200.parallel.peer import PeerGroup
+
+    regions = [None] * world
+    if backend == "cuda":
+        regions = PeerGroup.local(world, FixedEPLayer.peer_bytes(cfg, world, capacity))
+    return [
+        FixedEPLayer(cfg, r, world, *shard_experts(w13, w2, r, world), capacity=capacity, backend=backend,
+                     peer_region=regions[r], wait_ns=50_000_000, **kw)
+        for r in range(world)
+    ]
+
+
+def _inputs(cfg, world, tokens, seed, dist="uniform"):
+    xs = [make_hidden(t, cfg, seed + r, device="cuda") for r, t in enumerate(tokens)]
+    lgs = [make_logits(t, cfg, seed + 100 + r, dist=dist, device="cuda") for r, t in enumerate(tokens)]
+    return xs, lgs
+
+
+def _ok(layer):
+    st = layer.check_status()
+    assert st["code"] == 0, st
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("dist", ["uniform", "hotspot"])
+def test_dispatch_rows_bitwise_equal_torch_twin(world, dist):
+    cfg = SMALL_GPU
+    cap = 16
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    tokens = [cap, 5, 0, 11][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 7, dist)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"skip_payload": 0})
+    tw = _layers(cfg, world, cap, w13, w2, "torch")
+    nv = torch.tensor(3, device="cuda", dtype=torch.int32)
+    for use_nv in (False, True):
+        hits_c = [ly.stage_pack(x, lg, bias, nv if use_nv else None).clone() for ly, x, lg in zip(cu, xs, lgs)]
+        hits_t = [ly.stage_pack(x, lg, bias, nv if use_nv else None) for ly, x, lg in zip(tw, xs, lgs)]
+        torch.cuda.synchronize()
+        for d in range(world):
+            for s in range(world):
+                tw[d]._recv_store[s].copy_(tw[s]._send_store[d])
+        for r in range(world):
+            assert torch.equal(hits_c[r].bool(), hits_t[r].bool())
+            meta_c = cu[r]._meta_view(cu[r]._recv_store)
+            meta_t = tw[r]._meta_view(tw[r]._recv_store)
+            assert torch.equal(meta_c, meta_t)
+            for s in range(world):
+                t = tokens[s]
+                assert bitwise_equal(cu[r].recv[s, :t, : cfg.hidden_size].contiguous(),
+                                     tw[r].recv[s, :t, : cfg.hidden_size].contiguous())
+
+
+@pytest.mark.parametrize("world,cap", [(1, 8), (2, 16), (4, 32)])
+def test_expert_meta_matches_torch_layout(world, cap):
+    cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4)
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    tokens = [cap, cap // 2, 1, 0][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 3)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    for ly, x, lg in zip(cu, xs, lgs):
+        ly.stage_pack(x, lg, None)
+    for ly in cu:
+        ly._cuda_meta()
+        torch.cuda.synchronize()
+        _ok(ly)
+        _, local, wts = ly.received_routing()
+        order, offsets, inv, entry_row, entry_slot = ly._torch_layout(local)
+        n = int(offsets[-1])
+        assert torch.equal(ly.offsets.long(), offsets)
+        assert torch.equal(ly.entry_row[:n].long(), entry_row[:n])
+        assert torch.equal(ly.entry_slot[:n].long(), entry_slot[:n])
+        assert torch.equal(ly.inv.long(), inv)
+        assert torch.equal(ly.entry_w[:n], wts[entry_row[:n], entry_slot[:n]])
+        plan = ly.plan.tolist()
+        counts = (offsets[1:] - offsets[:-1]).tolist()
+        tiles = [(e, int(offsets[e]) + s, min(ly.block_m, c - s)) for e, c in enumerate(counts) for s in range(0, c, ly.block_m)]
+        assert plan[0] == len(tiles) and plan[3] == n
+        got = list(zip(ly.tile_e[: plan[0]].tolist(), ly.tile_s[: plan[0]].tolist(), ly.tile_n[: plan[0]].tolist()))
+        assert got == tiles
+        assert plan[1] in (1, 2, 4, 8) and plan[2] in (1, 2, 4, 8)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("dist", ["uniform", "zipf", "hotspot"])
+def test_layer_matches_oracle_and_twin(world, dist):
+    cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4, moe_intermediate_size=256)
+    cap = 16
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    tokens = [cap, 7, 0, 3][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 21, dist)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    tw = _layers(cfg, world, cap, w13, w2, "torch")
+    out_c = simulate_fixed(cu, xs, lgs, bias)
+    out_t = simulate_fixed(tw, xs, lgs, bias)
+    torch.cuda.synchronize()
+    for r in range(world):
+        _ok(cu[r])
+        t = tokens[r]
+        assert out_c[r][t:].abs().sum() == 0, "padding rows must be exactly zero"
+        if t == 0:
+            continue
+        ref = moe_reference(xs[r].cpu(), lgs[r].cpu(), bias.cpu(), w13.cpu(), w2.cpu(), cfg)
+        err = normwise_rel_err(out_c[r][:t].cpu(), ref)
+        err_twin = normwise_rel_err(out_t[r][:t].cpu(), ref)
+        assert err < gemm_tolerance(err_twin), (err, err_twin)
+
+
+def test_owner_reduce_and_combine_bitwise_given_same_y():
+    """With the same expert outputs y, return rows and the combined output equal the torch twin bitwise."""
+    world, cap = 2, 8
+    cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=4)
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    xs, lgs = _inputs(cfg, world, [cap, 5], 5)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    hits = [ly.stage_pack(x, lg, None).clone() for ly, x, lg in zip(cu, xs, lgs)]
+    from moeflow_b200.fixed import _ordered_masked_sum, combine_partials
+
+    expected_ret = [torch.zeros_like(ly.ret_recv) for ly in cu]
+    for d, ly in enumerate(cu):
+        ly._cuda_experts()
+        torch.cuda.synchronize()
+        _ok(ly)
+        _, local, _ = ly.received_routing()
+        y = torch.cat([ly.y, ly.y.new_zeros(1, cfg.hidden_size)])
+        inv = ly.inv.long().view(world * cap, cfg.top_k)
+        part = _ordered_masked_sum(y[inv], local >= 0).bfloat16().view(world, cap, cfg.hidden_size)
+        valid = (local >= 0).any(-1).view(world, cap)
+        for s in range(world):
+            expected_ret[s][d][valid[s]] = part[s][valid[s]]
+    for s, ly in enumerate(cu):
+        valid_rows = hits[s].bool().t()  # [R, C]
+        assert bitwise_equal(ly.ret_recv[valid_rows], expected_ret[s][valid_rows])
+        out = ly.stage_combine(hits[s], torch.bfloat16)
+        ref = combine_partials(ly.ret_recv, hits[s], torch.bfloat16)
+        torch.cuda.synchronize()
+        assert bitwise_equal(out, ref)
+
+
+def test_ring_combine_rounding_witness():
+    """[1, 256, 1, -256] summed in bf16 ring order from each source rank gives [1, 2, 2, 0]."""
+    world, cap = 4, 1
+    cfg = SMALL_GPU
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    outs = []
+    for rank in range(world):
+        from moeflow_b200.parallel.peer import PeerGroup
+
+        region = PeerGroup.local(world, FixedEPLayer.peer_bytes(cfg, world, cap))[rank]
+        ly = FixedEPLayer(cfg, rank, world, *shard_experts(w13, w2, rank, world), capacity=cap, backend="cuda",
+                          peer_region=region, combine_mode="bf16_ring", wait_ns=50_000_000)
+        vals = torch.tensor([1.0, 256.0, 1.0, -256.0], device="cuda")
+        ly.ret_recv.copy_(vals.view(world, 1, 1).expand(world, cap, cfg.hidden_size).bfloat16())
+        ly.hit.fill_(1)
+        ly._ret_flags.fill_(0)
+        outs.append(float(ly.stage_combine(ly.hit, torch.bfloat16)[0, 0]))
+        from moeflow_b200.fixed import combine_partials
+
+        twin = combine_partials(ly.ret_recv, ly.hit, torch.bfloat16, rank, "bf16_ring")
+        assert bitwise_equal(ly.out, twin)
+    assert outs == [1.0, 2.0, 2.0, 0.0]
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_graph_replay_with_changing_inputs(world):
+    """Capture each rank's stages in CUDA graphs, replay with new inputs and valid prefixes."""
+    cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=2)
+    cap = 8
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    tw = _layers(cfg, world, cap, w13, w2, "torch")
+    xs = [torch.zeros(cap, cfg.hidden_size, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    lgs = [torch.zeros(cap, cfg.n_routed_experts, device="cuda") for _ in range(world)]
+    nvs = [torch.full((), cap, dtype=torch.int32, device="cuda") for _ in range(world)]
+    # warm up (loads kernels, sets shared-memory attributes) before capture
+    simulate_fixed(cu, xs, lgs, bias, nvs)
+    torch.cuda.synchronize()
+    g_pack, g_exp, g_comb = [], [], []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for r, ly in enumerate(cu):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ly.stage_pack(xs[r], lgs[r], bias, nvs[r])
+            g_pack.append(g)
+        for ly in cu:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ly.stage_experts()
+            g_exp.append(g)
+        for ly in cu:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ly.stage_combine(ly.hit, torch.bfloat16)
+            g_comb.append(g)
+    torch.cuda.synchronize()
+    gen = torch.Generator().manual_seed(0)
+    for it in range(50):
+        for r in range(world):
+            xs[r].copy_(make_hidden(cap, cfg, 1000 + it * 7 + r))
+            lgs[r].copy_(make_logits(cap, cfg, 2000 + it * 7 + r))
+            nvs[r].fill_(int(torch.randint(0, cap + 1, (1,), generator=gen)))
+        for g in g_pack + g_exp + g_comb:
+            g.replay()
+        ref = simulate_fixed(tw, xs, lgs, bias, nvs)
+        torch.cuda.synchronize()
+        for r in range(world):
+            _ok(cu[r])
+            n = int(nvs[r])
+            assert cu[r].out[n:].abs().sum() == 0
+            if n:
+                err = normwise_rel_err(cu[r].out[:n], ref[r][:n].float())
+                assert err < 4 * 2.0**-8, (it, r, err)
+    del g_pack, g_exp, g_comb

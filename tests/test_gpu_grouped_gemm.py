@@ -1,0 +1,136 @@
+"""tcgen05 grouped GEMMs (gate/up + SwiGLU, down + row scale) against plain fp32 PyTorch."""
+
+import pytest
+import torch
+
+from moeflow_b200.experts import swiglu_clamp
+from moeflow_b200.tolerances import normwise_rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _status_ok(status):
+    from moeflow_b200.ops._lib import decode_status
+
+    st = decode_status(int(status.item()))
+    assert st["code"] == 0, st
+
+
+def _problem(counts, hidden, inter, seed=0, scale_x=1.0):
+    g = torch.Generator().manual_seed(seed)
+    n_exp = len(counts)
+    n = sum(counts)
+    w13 = (torch.randn(n_exp, 2 * inter, hidden, generator=g) * (2.0 / hidden**0.5)).bfloat16().cuda()
+    w2 = (torch.randn(n_exp, hidden, inter, generator=g) / inter**0.5).bfloat16().cuda()
+    n_src = max(n, 1) + 5
+    x = (torch.randn(n_src, hidden, generator=g) * scale_x).bfloat16().cuda()
+    row_index = torch.randint(0, n_src, (max(n, 1),), generator=g).int().cuda()
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    scale = torch.rand(max(n, 1), generator=g).float().cuda() + 0.5
+    return w13, w2, x, row_index, offsets, scale
+
+
+def _ref_gate_up(x, row_index, w13, offsets, limit):
+    rows = x[row_index.long()].float()
+    out = torch.zeros(offsets[-1], w13.shape[1] // 2, device=x.device)
+    for e, (lo, hi) in enumerate(zip(offsets[:-1], offsets[1:])):
+        if hi > lo:
+            h = rows[lo:hi] @ w13[e].float().t()
+            out[lo:hi] = swiglu_clamp(h, limit)
+    return out
+
+
+def _ref_down(act, w2, offsets, scale):
+    out = torch.zeros(offsets[-1], w2.shape[1], device=act.device)
+    for e, (lo, hi) in enumerate(zip(offsets[:-1], offsets[1:])):
+        if hi > lo:
+            out[lo:hi] = (act[lo:hi].float() @ w2[e].float().t()) * scale[lo:hi, None]
+    return out
+
+
+CASES = [
+    ([1], 256, 128, 64),
+    ([3, 0, 17, 5], 512, 256, 64),
+    ([16, 64, 1, 0, 33], 1024, 384, 64),
+    ([70, 2, 130], 512, 128, 64),  # experts longer than one tile
+    ([5, 9], 512, 256, 32),
+    ([100, 20], 512, 256, 128),
+]
+
+
+@pytest.mark.parametrize("counts,hidden,inter,block_m", CASES)
+@pytest.mark.parametrize("split", [1, 2, 4])
+def test_gate_up_and_down(counts, hidden, inter, block_m, split):
+    from moeflow_b200.ops.grouped_gemm import down_proj, gate_up_swiglu, plan_from_offsets
+
+    if (inter // 64) % split:
+        pytest.skip("split does not divide the K blocks of the down GEMM")
+    w13, w2, x, row_index, offsets, scale = _problem(counts, hidden, inter, seed=len(counts) + hidden)
+    n = offsets[-1]
+    tp = plan_from_offsets(offsets, block_m, x.device)
+    status = torch.zeros(1, dtype=torch.int64, device=x.device)
+    act = gate_up_swiglu(x, w13, tp, row_index=row_index[:n], limit=10.0, split=split, status=status, wait_ns=50_000_000)
+    torch.cuda.synchronize()
+    _status_ok(status)
+    ref_act = _ref_gate_up(x, row_index[:n], w13, offsets, 10.0)
+    assert normwise_rel_err(act, ref_act) < 4 * 2.0**-8, normwise_rel_err(act, ref_act)
+
+    y = down_proj(act, w2, tp, row_scale=scale[:n], split=split, status=status, wait_ns=50_000_000)
+    torch.cuda.synchronize()
+    _status_ok(status)
+    ref_y = _ref_down(act, w2, offsets, scale[:n])
+    assert normwise_rel_err(y, ref_y) < 4 * 2.0**-8, normwise_rel_err(y, ref_y)
+    # bf16 rounding of an fp32 result: element-wise within one bf16 ulp plus fp32 summation noise
+    assert (y.float() - ref_y).abs().max() <= 2.0**-7 * ref_y.abs().max() + 1e-3
+
+
+def test_clamp_is_exercised_and_identity_rows():
+    from moeflow_b200.ops.grouped_gemm import gate_up_swiglu, plan_from_offsets
+
+    w13, _, x, _, offsets, _ = _problem([20, 12], 256, 128, seed=5, scale_x=8.0)
+    tp = plan_from_offsets(offsets, 64, x.device)
+    status = torch.zeros(1, dtype=torch.int64, device=x.device)
+    ident = torch.arange(offsets[-1], dtype=torch.int32, device=x.device)
+    act = gate_up_swiglu(x, w13, tp, row_index=None, limit=2.0, status=status, wait_ns=50_000_000)
+    torch.cuda.synchronize()
+    _status_ok(status)
+    ref = _ref_gate_up(x, ident, w13, offsets, 2.0)
+    h = x[: offsets[-1]].float() @ w13[0].float().t()
+    assert (h.abs() > 2.0).any(), "inputs do not reach the clamp"
+    assert normwise_rel_err(act, ref) < 4 * 2.0**-8
+    act_r = gate_up_swiglu(x, w13, tp, row_index=None, limit=2.0, round_h=True, status=status, wait_ns=50_000_000)
+    ref_r = torch.zeros_like(ref)
+    for e, (lo, hi) in enumerate(zip(offsets[:-1], offsets[1:])):
+        ref_r[lo:hi] = swiglu_clamp((x[lo:hi].float() @ w13[e].float().t()).bfloat16(), 2.0).float()
+    torch.cuda.synchronize()
+    assert normwise_rel_err(act_r, ref_r) < 4 * 2.0**-8
+
+
+def test_split_k_is_deterministic():
+    from moeflow_b200.ops.grouped_gemm import gate_up_swiglu, plan_from_offsets
+
+    w13, _, x, row_index, offsets, _ = _problem([9, 30, 4], 1024, 256, seed=9)
+    tp = plan_from_offsets(offsets, 64, x.device)
+    runs = [gate_up_swiglu(x, w13, tp, row_index=row_index[: offsets[-1]], split=4).clone() for _ in range(5)]
+    torch.cuda.synchronize()
+    for r in runs[1:]:
+        assert torch.equal(r.view(torch.int16), runs[0].view(torch.int16))
+
+
+@pytest.mark.slow
+def test_glm_shape_one_expert_tile():
+    from moeflow_b200.ops.grouped_gemm import down_proj, gate_up_swiglu, plan_from_offsets
+
+    w13, w2, x, row_index, offsets, scale = _problem([7, 0, 21], 4096, 1536, seed=2)
+    n = offsets[-1]
+    tp = plan_from_offsets(offsets, 64, x.device)
+    status = torch.zeros(1, dtype=torch.int64, device=x.device)
+    act = gate_up_swiglu(x, w13, tp, row_index=row_index[:n], status=status, split=2)
+    y = down_proj(act, w2, tp, row_scale=scale[:n], status=status, split=2)
+    torch.cuda.synchronize()
+    _status_ok(status)
+    ref_act = _ref_gate_up(x, row_index[:n], w13, offsets, 10.0)
+    assert normwise_rel_err(act, ref_act) < 4 * 2.0**-8
+    assert normwise_rel_err(y, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8

@@ -1,0 +1,65 @@
+"""Router top-k and RMSNorm kernels against their PyTorch / loop-level definitions."""
+
+import pytest
+import torch
+
+from conftest import replace
+from moeflow_b200 import GLM53_FLASH, MoEConfig
+from moeflow_b200.reference import route_reference
+from moeflow_b200.router import route
+from moeflow_b200.testing import make_bias, make_logits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dist", ["uniform", "zipf", "hotspot"])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_router_kernel_matches_torch_and_oracle(dist, with_bias):
+    from moeflow_b200.ops.kernels import router_topk
+
+    cfg = GLM53_FLASH
+    logits = make_logits(37, cfg, 3, dist=dist)
+    bias = make_bias(cfg, 4) if with_bias else None
+    w_ref, ids_ref = route(logits, bias, cfg)
+    w, ids = router_topk(logits.cuda(), None if bias is None else bias.cuda(), cfg)
+    assert torch.equal(ids.cpu(), ids_ref)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-7)
+    oracle = route_reference(logits[:6], bias, cfg)
+    for t, r in enumerate(oracle):
+        assert [e for e, _ in r] == ids[t].tolist()
+        torch.testing.assert_close(w[t].cpu().double(), torch.tensor([v for _, v in r]).double(), rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("scoring", ["sigmoid", "softmax"])
+def test_router_kernel_groups_and_ties(scoring):
+    from moeflow_b200.ops.kernels import router_topk
+
+    cfg = MoEConfig(n_routed_experts=64, top_k=6, n_group=8, topk_group=3, scoring_func=scoring)
+    logits = make_logits(50, cfg, 11)
+    logits[0, :] = 0.25  # all equal: lower ids win
+    logits[1, 10:20] = 3.0
+    bias = make_bias(cfg, 12)
+    for b in (bias, None):
+        w_ref, ids_ref = route(logits, b, cfg)
+        w, ids = router_topk(logits.cuda(), None if b is None else b.cuda(), cfg)
+        assert torch.equal(ids.cpu(), ids_ref)
+        torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-7)
+    cfg2 = replace(cfg, n_group=1, topk_group=1, norm_topk_prob=False)
+    w_ref, ids_ref = route(logits, None, cfg2)
+    w, ids = router_topk(logits.cuda(), None, cfg2)
+    assert torch.equal(ids.cpu(), ids_ref)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (33, 4096), (7, 256)])
+def test_rmsnorm_kernel(rows, hidden):
+    from moeflow_b200.ops.kernels import rmsnorm
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, hidden, generator=g).bfloat16().cuda()
+    gamma = (1.0 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().cuda()
+    out = rmsnorm(x, gamma, 1e-6)
+    xf = x.float()
+    ref = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()).bfloat16()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=1e-2, atol=1e-2)
+    assert (out.float() - ref.float()).abs().max() <= 2 * 2.0**-8 * ref.float().abs().max()
