@@ -1,0 +1,415 @@
+"""Headline benchmark: routed MoE layer latency under CUDA-graph replay, max over ranks.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Config (fixed by the baseline): one GLM-5.3-Flash routed MoE layer in bf16 — hidden 4096, 288 routed
+experts, top-8, SwiGLU expert intermediate 1536 — random-init weights, synthetic tokens, uniform
+routing, EP = N ranks, T tokens per rank (headline T = 128; the sweep covers 1..128).  One step is one
+complete routed layer (router logits -> top-k -> dispatch -> experts -> return -> weighted merge)
+replayed from a CUDA graph.
+
+Timing protocol (both arms): W warm-up steps, then exactly K timed steps.  Before every step, outside
+the timed interval, the next input set of a rotating pool is copied into the static input buffers and
+a 256 MiB buffer is written to flush L2; ranks are aligned with a barrier; the step is bracketed by CUDA
+events on the launching stream; the per-rank sum over the K steps is reduced with MAX over ranks.
+SM clocks and throttle reasons are sampled with nvidia-smi while the steps run.
+
+``e2e`` repeats the measurement through the public serving call (``GraphedMoELayer.__call__``): every
+step copies that step's hidden states and logits from pinned host memory, replays, and copies the
+output rows back to pinned host memory, all inside the timed interval.
+
+``--impl reference`` runs the unmodified reference (installed under baseline/_ref) through its own
+``FixedEPLayer(..., metadata_kernel, fused_reduce, fused_combine, fused_dispatch).forward`` with NCCL
+all-to-alls and Triton kernels, under the same protocol.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent
+HIDDEN, INTER, EXPERTS, TOP_K = 4096, 1536, 288, 8
+SWEEP = (1, 2, 4, 8, 16, 32, 64, 128)
+PUBLISHED_US = {(4, 128): 740.8, (4, 8): 461.7, (4, 1): 144.2}  # reference README, EP=4, I=2048, real weights
+POOL = 4  # rotating input sets
+
+
+# ------------------------------------------------------------------------------------------------
+# environment
+# ------------------------------------------------------------------------------------------------
+def init_dist(n_gpus: int) -> tuple[int, int, torch.device]:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != n_gpus:
+        if world == 1 and n_gpus > 1:
+            raise SystemExit(f"--gpus {n_gpus} needs torch.distributed.run with --nproc-per-node {n_gpus}")
+        raise SystemExit(f"--gpus {n_gpus} does not match WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    return rank, world, dev
+
+
+def init_single_process_group(dev: torch.device) -> None:
+    """World-1 NCCL group for code that calls collectives unconditionally (the reference does)."""
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(29000 + os.getpid() % 2000))
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=0, world_size=1, device_id=dev)
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples of one GPU while the timed region runs (read-only queries)."""
+
+    FIELDS = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {
+            "sm_mhz": sm[len(sm) // 2] if sm else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic data (device-side generation; identical recipe for both arms)
+# ------------------------------------------------------------------------------------------------
+def make_local_weights(rank: int, world: int, dev: torch.device):
+    """Local expert shard, N(0, (2/sqrt(H))^2) / N(0, (1/sqrt(I))^2), generated expert by expert."""
+    local = EXPERTS // world
+    w13 = torch.empty(local, 2 * INTER, HIDDEN, dtype=torch.bfloat16, device=dev)
+    w2 = torch.empty(local, HIDDEN, INTER, dtype=torch.bfloat16, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    for e in range(local):
+        w13[e] = (torch.randn(2 * INTER, HIDDEN, generator=g, device=dev) * (2.0 / math.sqrt(HIDDEN))).to(torch.bfloat16)
+        w2[e] = (torch.randn(HIDDEN, INTER, generator=g, device=dev) * (1.0 / math.sqrt(INTER))).to(torch.bfloat16)
+    return w13, w2
+
+
+def make_inputs(tokens: int, rank: int, pool: int, pinned: bool):
+    """``pool`` input sets of hidden states ``[T, H]`` bf16 and uniform router logits ``[T, E]`` fp32 (host)."""
+    xs, lgs = [], []
+    for i in range(pool):
+        g = torch.Generator().manual_seed(7919 * tokens + 104729 * rank + i)
+        x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16)
+        lg = torch.randn(tokens, EXPERTS, generator=g)
+        if pinned:
+            x, lg = x.pin_memory(), lg.pin_memory()
+        xs.append(x)
+        lgs.append(lg)
+    return xs, lgs
+
+
+# ------------------------------------------------------------------------------------------------
+# arms: each returns an object with .x .logits (static device inputs), .replay(), .call(x, lg, out), .launches
+# ------------------------------------------------------------------------------------------------
+class OurArm:
+    name = "moeflow_b200"
+
+    def __init__(self, rank, world, dev, w13, w2, bias, tokens):
+        from moeflow_b200 import GLM53_FLASH_I1536
+        from moeflow_b200.fixed import FixedEPLayer
+        from moeflow_b200.models.routed_moe import GraphedMoELayer
+        from moeflow_b200.ops import _lib
+
+        _lib.lib()  # the native library is mandatory here
+        self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, w13, w2, capacity=tokens, backend="cuda")
+        self.g = GraphedMoELayer(self.layer, bias).capture()
+        self.x, self.logits = self.g.x, self.g.logits
+        self.launches = self.g.kernels_per_step
+
+    def replay(self):
+        return self.g.replay()
+
+    def call(self, x, lg, out):
+        return self.g(x, lg, out)
+
+    def check(self):
+        st = self.layer.check_status()
+        if st["code"] != 0:
+            raise RuntimeError(f"device status: {st}")
+
+    def close(self):
+        self.g.close()
+
+
+class ReferenceArm:
+    name = "reference"
+
+    def __init__(self, rank, world, dev, w13, w2, bias, tokens):
+        sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+        from moeflow.config import MoEConfig as RefConfig  # type: ignore
+        from moeflow.fixed import FixedEPLayer as RefLayer  # type: ignore
+
+        cfg = RefConfig(hidden_size=HIDDEN, moe_intermediate_size=INTER, n_routed_experts=EXPERTS, top_k=TOP_K)
+        self.layer = RefLayer(cfg, rank, world, w13, w2, capacity=tokens, metadata_kernel=True, fused_reduce=True,
+                              fused_combine=True, fused_dispatch=True)
+        self.bias = bias
+        self.x = torch.zeros(tokens, HIDDEN, dtype=torch.bfloat16, device=dev)
+        self.logits = torch.zeros(tokens, EXPERTS, dtype=torch.float32, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.layer.forward(self.x, self.logits, self.bias)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = self.layer.forward(self.x, self.logits, self.bias)
+        torch.cuda.synchronize()
+        self.launches = None
+
+    def replay(self):
+        self.graph.replay()
+        return self.out
+
+    def call(self, x, lg, out):
+        self.x.copy_(x, non_blocking=True)
+        self.logits.copy_(lg, non_blocking=True)
+        self.graph.replay()
+        out.copy_(self.out, non_blocking=True)
+        return out
+
+    def check(self):
+        pass
+
+    def close(self):
+        self.graph = None
+
+
+# ------------------------------------------------------------------------------------------------
+# timing
+# ------------------------------------------------------------------------------------------------
+def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush: torch.Tensor) -> float:
+    """Sum of the device times of ``steps`` steps in ms (this rank).  prepare_fn(i) runs untimed."""
+    for i in range(warmup):
+        prepare_fn(i)
+        flush.zero_()
+        step_fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        prepare_fn(warmup + i)
+        flush.zero_()
+        if world > 1:
+            dist.barrier()
+        starts[i].record()
+        step_fn(warmup + i)
+        ends[i].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    return sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+
+
+def max_over_ranks(v: float, world: int, dev) -> float:
+    if world == 1:
+        return v
+    t = torch.tensor([v], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def measure(arm_cls, rank, world, dev, w13, w2, bias, tokens, steps, warmup, flush):
+    arm = arm_cls(rank, world, dev, w13, w2, bias, tokens)
+    xs_h, lgs_h = make_inputs(tokens, rank, POOL, pinned=True)
+    xs_d = [x.to(dev) for x in xs_h]
+    lgs_d = [lg.to(dev) for lg in lgs_h]
+    out_h = torch.empty(tokens, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    def prepare(i):
+        arm.x.copy_(xs_d[i % POOL])
+        arm.logits.copy_(lgs_d[i % POOL])
+
+    dev_ms = timed_steps(lambda i: arm.replay(), prepare, steps, warmup, world, flush)
+    arm.check()
+    e2e_ms = timed_steps(lambda i: arm.call(xs_h[i % POOL], lgs_h[i % POOL], out_h), lambda i: None, steps, warmup,
+                         world, flush)
+    arm.check()
+    finite = bool(torch.isfinite(out_h.float()).all())
+    res = {
+        "us_per_step": max_over_ranks(dev_ms, world, dev) * 1e3 / steps,
+        "e2e_us_per_step": max_over_ranks(e2e_ms, world, dev) * 1e3 / steps,
+        "launches_per_step": arm.launches,
+        "finite": finite,
+        "h2d_bytes": tokens * HIDDEN * 2 + tokens * EXPERTS * 4,
+        "d2h_bytes": tokens * HIDDEN * 2,
+    }
+    arm.close()
+    del arm
+    torch.cuda.synchronize()
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="moeflow_b200", choices=["moeflow_b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=128, help="headline tokens per rank")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the T = 1..128 sweep")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "moeflow" / "fixed.py").exists():
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of /root/reference)"}))
+        return
+    rank, world, dev = init_dist(args.gpus)
+    if args.impl == "reference":
+        try:
+            import triton  # noqa: F401
+        except Exception as exc:  # pragma: no cover
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"triton not importable: {exc}"[:200]}))
+            return
+        init_single_process_group(dev)
+    arm_cls = ReferenceArm if args.impl == "reference" else OurArm
+
+    w13, w2 = make_local_weights(rank, world, dev)
+    bias = (0.05 * torch.randn(EXPERTS, generator=torch.Generator().manual_seed(99))).to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    try:
+        head = measure(arm_cls, rank, world, dev, w13, w2, bias, args.tokens, args.steps, args.warmup, flush)
+    except Exception as exc:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+            return
+        raise
+    clocks = sampler.stop() if rank == 0 else {}
+    per_t = {}
+    if not args.no_sweep:
+        for t in SWEEP:
+            if t == args.tokens:
+                per_t[str(t)] = round(head["us_per_step"], 2)
+                continue
+            try:
+                r = measure(arm_cls, rank, world, dev, w13, w2, bias, t, args.steps, args.warmup, flush)
+                per_t[str(t)] = round(r["us_per_step"], 2)
+            except Exception as exc:  # a sweep point never hides the headline
+                per_t[str(t)] = f"failed: {type(exc).__name__}"
+    if rank == 0:
+        pub = PUBLISHED_US.get((world, args.tokens))
+        launches = head["launches_per_step"]
+        line = {
+            "metric": "routed_moe_layer_us_per_step_graph_replay_max_over_ranks",
+            "value": round(head["us_per_step"], 3),
+            "unit": "us/step",
+            "impl": args.impl,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(head["us_per_step"] / 1e3, 6),
+            "higher_is_better": False,
+            "scaling": "weak",
+            "vs_baseline": round(head["us_per_step"] / pub, 4) if pub else None,
+            "dtype": "bf16",
+            "data": "synthetic tokens and uniform router logits, random-init weights N(0, 0.02-scale) of the named shape",
+            "config": {
+                "model": "GLM-5.3-Flash routed MoE layer (hidden 4096, 288 experts, top-8, intermediate 1536)",
+                "global_batch": args.tokens * world,
+                "tokens_per_rank": args.tokens,
+                "seq_len": 1,
+                "parallelism": f"ep{world}",
+                "routing": "uniform",
+                "l2": "256 MiB buffer written before every timed step (L2 flush); local expert weights >> L2",
+                "timing": "per-step CUDA events, barrier-aligned, sum over steps, max over ranks",
+                "published_baseline_note": "published number is EP=4, intermediate 2048, real weights, L2-warm replays",
+            },
+            "per_T_us": per_t,
+            "e2e": {
+                "value": round(head["e2e_us_per_step"], 3),
+                "unit": "us/step",
+                "h2d_bytes_per_step": head["h2d_bytes"],
+                "d2h_bytes_per_step": head["d2h_bytes"],
+            },
+            "gpu_launches": (launches * args.steps) if launches else None,
+            "finite": head["finite"],
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
