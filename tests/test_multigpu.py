@@ -1,0 +1,39 @@
+"""Multi-GPU checks, launched as child processes with torch.distributed.run on 127.0.0.1."""
+
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(n: int, script: str, *extra: str, timeout: int = 600) -> dict:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "multigpu" / script), *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert res.returncode == 0 and lines, f"rc={res.returncode}\n{res.stdout[-3000:]}\n{res.stderr[-3000:]}"
+    return json.loads(lines[-1])
+
+
+@pytest.mark.parametrize("dist_name", ["uniform", "hotspot"])
+def test_fused_layer_over_peer_memory(dist_name):
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    out = _launch(n, "fixed_peer_check.py", "--dist", dist_name, "--iters", "12", "--replays", "120")
+    assert out["ok"], out
