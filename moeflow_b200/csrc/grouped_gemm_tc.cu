@@ -454,3 +454,69 @@ int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid
 }
 
 }  // extern "C"
+
+// -------------------------------------------------------------------------------------------------
+// Down projection without any allocation (declared in moeflow_b200.h, MF_STATIC_SCRATCH_* limits).
+//
+// The split-K scratch (fp32 partial sums, then the arrival counters) lives in the file-scope device
+// array below instead of a caller-provided buffer.  Every GPU that loads this library holds the array
+// until the process exits.  In host code the array's name is only a stand-in for the symbol; the
+// device address comes from cudaGetSymbolAddress, taken once per device with that device current.
+// -------------------------------------------------------------------------------------------------
+namespace mf {
+
+constexpr int kStaticNMax = 64;                                             // token rows per tile
+constexpr size_t kStaticSlotFloats = (size_t)kStaticNMax * kBlockM;         // one accumulator tile
+constexpr size_t kStaticPartialBytes = (size_t)MF_STATIC_SCRATCH_MAX_SLOTS * kStaticSlotFloats * sizeof(float);
+constexpr size_t kStaticCounterBytes = (size_t)MF_STATIC_SCRATCH_MAX_COUNTERS * sizeof(int);
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+}  // namespace mf
+
+extern "C" int mf_gemm_down_static_scratch(const void* tmap, const mf_gemm_args* args, int max_tiles, int split,
+                                           int grid, mf_stream_t stream) {
+  using namespace mf;
+  if (!tmap || !args || grid < 1 || max_tiles < 1) return -1;
+  if (split != 1 && split != 2 && split != 4 && split != 8) return -2;
+  if (args->m_blocks < 1 || args->k_blocks < 1 || args->k_blocks % split != 0) return -3;
+  if ((args->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(args->b_base) & 15) != 0) return -4;
+  // Sizes beyond the static array are refused, never truncated.
+  const long long slots = (long long)max_tiles * args->m_blocks * split;
+  const long long counters = (long long)max_tiles * args->m_blocks * 4;
+  if (slots > MF_STATIC_SCRATCH_MAX_SLOTS) return -20;     // too many (tile, block, split) partial tiles
+  if (counters > MF_STATIC_SCRATCH_MAX_COUNTERS) return -21;
+
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -22;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // First call on this device: resolve the symbol and size the kernel's shared memory.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(grouped_gemm_kernel<false, kStaticNMax>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GemmCfg<false, kStaticNMax>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_addr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_static_scratch_addr[dev]);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the arrival counters must start at zero.
+  e = cudaMemsetAsync(base + kStaticPartialBytes, 0, (size_t)counters * sizeof(int), s);
+  if (e != cudaSuccess) return (int)e;
+
+  mf_gemm_args a = *args;
+  a.partial = reinterpret_cast<float*>(base);
+  a.counters = reinterpret_cast<int*>(base + kStaticPartialBytes);
+  a.max_split_slots = MF_STATIC_SCRATCH_MAX_SLOTS;
+  CUtensorMap tm;
+  memcpy(&tm, tmap, sizeof(tm));
+  grouped_gemm_kernel<false, kStaticNMax>
+      <<<grid, kThreads, GemmCfg<false, kStaticNMax>::kSmemBytes, s>>>(tm, a);
+  return (int)cudaGetLastError();
+}

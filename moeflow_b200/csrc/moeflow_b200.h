@@ -59,6 +59,37 @@ int mf_gemm_gate_up(const void* tmap, const mf_gemm_args* args, int n_max, int g
 int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);
 int mf_gemm_smem_bytes(int gate_up, int n_max);
 
+
+// ---- down projection for callers that cannot allocate -------------------------------------------------
+// No counterpart in the reference.
+//
+// Some callers of this library have no way to get device memory at call time: a C or C++ host that
+// does not link a tensor framework, or serving code that runs after the engine has handed every
+// free byte of the GPU to its KV-cache pool, where a cudaMalloc can fail or stall the whole device.
+// mf_gemm_down needs split-K scratch (fp32 partial tiles and arrival counters) that somebody has to
+// own; this variant owns it itself, in a device array that is part of the loaded library.
+//
+//  * It computes exactly what mf_gemm_down computes with n_max = 64 (token tiles of up to 64 rows):
+//    same kernel, same summation order, so the results are identical.  The caller still passes the
+//    inputs and outputs in `args` (operand rows, tile arrays, plan words, out, row_scale, status);
+//    args->partial, args->counters and args->max_split_slots are ignored.
+//  * `max_tiles` is the largest tile count the plan word MF_PLAN_N_TILES may hold and `split` the value
+//    of the plan word args->split_word (1, 2, 4 or 8).  The call is refused with a negative code, and
+//    nothing is launched, when max_tiles * m_blocks * split exceeds MF_STATIC_SCRATCH_MAX_SLOTS (-20)
+//    or max_tiles * m_blocks * 4 exceeds MF_STATIC_SCRATCH_MAX_COUNTERS (-21).
+//  * It calls no cudaMalloc / cudaFree and no allocating library routine.  The scratch array
+//    (MF_STATIC_SCRATCH_MAX_SLOTS * 32 KiB + MF_STATIC_SCRATCH_MAX_COUNTERS * 4 bytes, about 4.1 MiB) is
+//    held by every GPU that loads the library until the process exits.
+//  * The first call on a device resolves the array's device address and sets the kernel's shared-memory
+//    attribute; make that first call with the device current and before any stream capture begins.
+//  * All calls share the one array per device.  It keeps the previous call's contents; the entry point
+//    clears the arrival counters on `stream` before the launch.  Two calls that overlap on the same GPU
+//    (different streams, or different host threads) race on the array: serialise them.
+#define MF_STATIC_SCRATCH_MAX_SLOTS 128
+#define MF_STATIC_SCRATCH_MAX_COUNTERS 4096
+int mf_gemm_down_static_scratch(const void* tmap, const mf_gemm_args* args, int max_tiles, int split, int grid,
+                                mf_stream_t stream);
+
 // ---- router / norm --------------------------------------------------------------------------------
 int mf_router_topk(const float* logits, const float* bias, float* weights, int* ids, int tokens, int experts,
                    int top_k, int n_group, int topk_group, int sigmoid, int renorm, float scale,
