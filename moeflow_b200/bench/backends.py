@@ -1,0 +1,121 @@
+"""Benchmark backends: every class exposes ``run(x, logits) -> out [T, H]`` for one EP rank.
+
+``init_dist`` sets up ``torch.distributed`` with NCCL for device tensors and gloo for Python objects.
+``FusedFixedBackend`` is the product path (cuda backend, peer-memory transport); ``TorchFixedBackend`` is
+its PyTorch/NCCL twin; ``NaiveBackend`` is the variable-size pipeline with a host round trip.
+``ReferenceFixedBackend`` drives the reference's own ``FixedEPLayer`` when it is installed under
+``baseline/_ref``.  Counterpart of ``scripts/bench/backends.py:33-325`` (the vLLM-backed arms of that file
+need vLLM's modular-kernel objects and live in ``moeflow_b200.integrations``).
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ..comm import CollectiveRowExchange
+from ..config import MoEConfig
+from ..ep_moe import EPMoELayer
+from ..fixed import FixedEPLayer
+
+BACKENDS = ("fused", "torch_fixed", "naive", "reference_fixed")
+
+
+@dataclass
+class DistInfo:
+    rank: int
+    world: int
+    local_rank: int
+    device: torch.device
+
+
+def init_dist(timeout_s: int = 600) -> DistInfo:
+    """One process per GPU; rendezvous on 127.0.0.1 unless the launcher says otherwise."""
+    from datetime import timedelta
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        kw = {"device_id": device} if cuda else {}
+        dist.init_process_group("cpu:gloo,cuda:nccl" if cuda else "gloo", rank=rank, world_size=world,
+                                timeout=timedelta(seconds=timeout_s), **kw)
+    return DistInfo(rank, world, local, device)
+
+
+class FusedFixedBackend:
+    name = "fused"
+
+    def __init__(self, cfg: MoEConfig, info: DistInfo, w13_local, w2_local, bias, capacity: int, **layer_kw):
+        self.layer = FixedEPLayer(cfg, info.rank, info.world, w13_local, w2_local, capacity=capacity, backend="cuda",
+                                  **layer_kw)
+        self.bias = bias
+
+    def run(self, x, logits):
+        return self.layer.forward(x, logits, self.bias)[: x.shape[0]]
+
+
+class TorchFixedBackend:
+    name = "torch_fixed"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity, **layer_kw):
+        self.layer = FixedEPLayer(cfg, info.rank, info.world, w13_local, w2_local, capacity=capacity, backend="torch",
+                                  **layer_kw)
+        self.bias = bias
+
+    def run(self, x, logits):
+        return self.layer.forward(x, logits, self.bias)[: x.shape[0]]
+
+
+class NaiveBackend:
+    name = "naive"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity=None, **_):
+        self.layer = EPMoELayer(cfg, info.rank, info.world, w13_local, w2_local)
+        self.comm = CollectiveRowExchange()
+        self.bias = bias
+
+    def run(self, x, logits):
+        return self.layer.forward(x, logits, self.bias, self.comm)
+
+
+class ReferenceFixedBackend:
+    """The reference's own fixed layer with all four of its fusion switches (Triton + NCCL)."""
+
+    name = "reference_fixed"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity, **_):
+        root = Path(__file__).resolve().parents[2] / "baseline" / "_ref"
+        if not (root / "moeflow" / "fixed.py").exists():
+            raise RuntimeError("the reference is not installed under baseline/_ref")
+        if str(root) not in sys.path:
+            sys.path.insert(0, str(root))
+        from moeflow.config import MoEConfig as RefConfig  # type: ignore
+        from moeflow.fixed import FixedEPLayer as RefLayer  # type: ignore
+
+        ref_cfg = RefConfig(**cfg.to_dict())
+        self.layer = RefLayer(ref_cfg, info.rank, info.world, w13_local, w2_local, capacity=capacity,
+                              metadata_kernel=True, fused_reduce=True, fused_combine=True, fused_dispatch=True)
+        self.bias = bias
+
+    def run(self, x, logits):
+        return self.layer.forward(x, logits, self.bias)[: x.shape[0]]
+
+
+def make_backend(name: str, *args, **kw):
+    table = {"fused": FusedFixedBackend, "torch_fixed": TorchFixedBackend, "naive": NaiveBackend,
+             "reference_fixed": ReferenceFixedBackend}
+    if name not in table:
+        raise ValueError(f"unknown backend {name!r}; choose from {BACKENDS}")
+    return table[name](*args, **kw)

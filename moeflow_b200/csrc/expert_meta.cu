@@ -169,11 +169,15 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
     }
     const unsigned same = __match_any_sync(0xffffffffu, key);
     if (key >= 0) {
+      // pos < N always holds when the rows did not change between the two sweeps; the guard keeps a
+      // racing writer (a peer that runs ahead in a truncated stage-timing run) from causing a stray store.
       const int pos = offs[key] + my_hist[key] + __popc(same & ((1u << lane) - 1u));
-      a.entry_row[pos] = row;
-      a.entry_slot[pos] = slot;
-      a.entry_w[pos] = __int_as_float(wbits);
-      a.inv[i] = pos;
+      if (pos < N) {
+        a.entry_row[pos] = row;
+        a.entry_slot[pos] = slot;
+        a.entry_w[pos] = __int_as_float(wbits);
+      }
+      a.inv[i] = pos < N ? pos : -1;
     } else if (i < end) {
       a.inv[i] = -1;
     }

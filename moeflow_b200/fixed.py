@@ -38,6 +38,8 @@ from .experts import BatchedTorchExperts, TorchLoopExperts
 from .router import route
 
 STAGES = ("ROUTER", "DISPATCH", "A2A_FORWARD", "EXPERT", "A2A_RETURN", "COMBINE")
+#: Finer prefixes of the EXPERT stage that only the cuda backend can stop after (one per kernel).
+CUDA_SUBSTAGES = ("META", "GEMM1", "GEMM2")
 
 _DEFAULT_WAIT_NS = 2_000_000_000
 
@@ -362,7 +364,8 @@ class FixedEPLayer:
     def forward(self, x, logits, bias, num_valid: torch.Tensor | None = None, stop_after: str | None = None):
         """Whole layer; ``stop_after`` (one of ``STAGES``) truncates it for prefix-graph stage timing."""
         if stop_after is not None and stop_after not in STAGES:
-            raise ValueError(f"stop_after must be one of {STAGES}")
+            if not (self.backend == "cuda" and stop_after in CUDA_SUBSTAGES):
+                raise ValueError(f"stop_after must be one of {STAGES}")
         weights, ids = self.stage_route(logits, bias)
         if stop_after == "ROUTER":
             return weights
@@ -373,6 +376,9 @@ class FixedEPLayer:
             self._exchange(self._recv_store, self._send_store)
         if stop_after == "A2A_FORWARD":
             return self.recv
+        if stop_after in CUDA_SUBSTAGES:
+            self._cuda_experts(stop_after)
+            return self.plan
         self.stage_experts()
         if stop_after == "EXPERT":
             return self.ret_recv if self.backend == "cuda" else self.ret_send
@@ -534,15 +540,21 @@ class FixedEPLayer:
 
         _lib.check(self._lib.mf_expert_meta(C.byref(self._a_meta), _lib.stream_ptr()), "expert_meta")
 
-    def _cuda_experts(self) -> None:
+    def _cuda_experts(self, stop_after: str | None = None) -> None:
         from .ops import _lib
 
         if self._tmap13 is None:
             raise RuntimeError("no expert weights bound (set_weights)")
         s = _lib.stream_ptr()
         self._cuda_meta()
+        if stop_after == "META":
+            return
         _lib.check(self._lib.mf_gemm_gate_up(self._tmap13, C.byref(self._a_gemm1), self.block_m, self.n_sms, s), "gate/up gemm")
+        if stop_after == "GEMM1":
+            return
         _lib.check(self._lib.mf_gemm_down(self._tmap2, C.byref(self._a_gemm2), self.block_m, self.n_sms, s), "down gemm")
+        if stop_after == "GEMM2":
+            return
         _lib.check(self._lib.mf_owner_reduce_push(C.byref(self._a_reduce), s), "owner_reduce_push")
 
     def _cuda_push_partials(self, partials: torch.Tensor) -> None:
