@@ -518,6 +518,24 @@ class FixedEPLayer:
         self._tmap13 = make_weight_tmap(self.w13)
         self._tmap2 = make_weight_tmap(self.w2)
 
+    def make_weight_maps(self, w13_local: torch.Tensor, w2_local: torch.Tensor):
+        """TMA descriptors for a weight pair (build once per MoE layer, then pass to ``bind_weights``)."""
+        if self.backend != "cuda":
+            return None, None
+        from .ops.kernels import make_weight_tmap
+
+        return make_weight_tmap(w13_local), make_weight_tmap(w2_local)
+
+    def bind_weights(self, w13_local: torch.Tensor, w2_local: torch.Tensor, tmap13=None, tmap2=None) -> None:
+        """Point this (possibly shared) buffer set at one MoE layer's expert weights; no copies."""
+        if self.backend != "cuda":
+            self.w13, self.w2 = w13_local, w2_local
+            return
+        if tmap13 is None or tmap2 is None:
+            self.set_weights(w13_local, w2_local)
+            return
+        self.w13, self.w2, self._tmap13, self._tmap2 = w13_local, w2_local, tmap13, tmap2
+
     def _cuda_dispatch(self, x, weights, ids, num_valid) -> torch.Tensor:
         from .ops import _lib
 
