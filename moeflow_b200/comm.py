@@ -36,18 +36,22 @@ class CollectiveRowExchange:
         self.world = dist.get_world_size(group)
 
     def _a2a(self, out, inp, out_splits=None, in_splits=None):
-        backend = dist.get_backend(self.group)
-        if backend == "gloo" and (out_splits is not None or inp.device.type == "cpu"):
-            # gloo has no all_to_all_single for uneven splits on every build: use all_to_all of lists.
-            ins = list(inp.split(in_splits)) if in_splits is not None else list(inp.chunk(self.world))
-            outs = list(out.split(out_splits)) if out_splits is not None else list(out.chunk(self.world))
-            ins = [t.contiguous() for t in ins]
-            outs_c = [torch.empty_like(t) for t in outs]
-            dist.all_to_all(outs_c, ins, group=self.group)
-            for dst, src in zip(outs, outs_c):
-                dst.copy_(src)
+        try:
+            dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
             return
-        dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
+        except RuntimeError as exc:
+            if "does not support" not in str(exc):
+                raise
+        # Backend without an all-to-all: pairwise sends and receives.
+        ins = list(inp.split(in_splits)) if in_splits is not None else list(inp.chunk(self.world))
+        outs = list(out.split(out_splits)) if out_splits is not None else list(out.chunk(self.world))
+        outs[self.rank].copy_(ins[self.rank])
+        peers = [p for p in range(self.world) if p != self.rank]
+        to_global = (lambda p: dist.get_global_rank(self.group, p)) if self.group is not None else (lambda p: p)
+        pending = [dist.isend(ins[p].contiguous(), to_global(p), group=self.group) for p in peers]
+        pending += [dist.irecv(outs[p], to_global(p), group=self.group) for p in peers]
+        for req in pending:
+            req.wait()
 
     def exchange_counts(self, send_counts: torch.Tensor) -> torch.Tensor:
         recv_counts = torch.empty_like(send_counts)

@@ -324,13 +324,7 @@ class FixedEPLayer:
         if self.world == 1 and (self.group is None or not dist.is_initialized()):
             out.copy_(inp)
             return
-        try:
-            dist.all_to_all_single(out, inp, group=self.group)
-        except RuntimeError:
-            outs = [t.contiguous() for t in out.unbind(0)]
-            dist.all_to_all(outs, [t.contiguous() for t in inp.unbind(0)], group=self.group)
-            for dst, src in zip(out.unbind(0), outs):
-                dst.copy_(src)
+        dist.all_to_all_single(out, inp, group=self.group)
 
     def forward_routed(
         self,
