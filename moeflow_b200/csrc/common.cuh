@@ -56,6 +56,16 @@ __device__ __forceinline__ uint32_t lane_id() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream is still running; it must call grid_dep_wait()
+// before it touches anything the predecessor writes (the wait returns when the predecessor has
+// completed and its writes are visible).  grid_dep_launch() lets the *next* kernel start early.
+// Both are no-ops in a kernel launched the ordinary way.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // System-scope flag access (peer-visible memory).
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
@@ -262,4 +272,25 @@ struct alignas(16) U4 {
   uint32_t x, y, z, w;
 };
 
+}  // namespace mf
+
+// Host side: launch with or without the programmatic-serialization attribute.
+extern "C" int mf_pdl_enabled(void);
+
+namespace mf {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool dependent, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (dependent && mf_pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 }  // namespace mf

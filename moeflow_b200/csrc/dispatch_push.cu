@@ -15,6 +15,7 @@
 // (moeflow/kernels/dispatch_pack.py:10-95, moeflow/fixed.py:95-125,234).
 #include "common.cuh"
 #include "moeflow_b200.h"
+#include "router.cuh"
 
 namespace mf {
 
@@ -28,15 +29,34 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
 
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
+  grid_dep_launch();  // the metadata kernel may get resident now; it waits for this grid to complete
   const unsigned epoch_next = *a.epoch + 1u;
   const bool has_token = t < a.T;
   const bool live = has_token && (a.num_valid == nullptr || t < *a.num_valid);
 
-  if (tid < a.K) {
+  if (a.logits != nullptr) {
+    // Fused routing: warp 0 routes this CTA's token; the other warps go on to load the hidden row.
+    extern __shared__ float s_route[];
+    if (tid < 32) {
+      float w = 0.f;
+      int id = -1;
+      if (has_token) {
+        const RouteParams p{a.E, a.K, a.n_group, a.topk_group, a.sigmoid, a.renorm, a.scale};
+        route_token_warp(a.logits + (size_t)t * a.E, a.bias, s_route, s_route + a.E, p, tid, w, id);
+      }
+      if (tid < a.K) {
+        s_id[tid] = has_token ? id : -1;
+        s_w[tid] = has_token ? w : 0.f;
+        if (has_token) {
+          a.route_w[(size_t)t * a.K + tid] = w;
+          a.route_ids[(size_t)t * a.K + tid] = id;
+        }
+      }
+    }
+  } else if (tid < a.K) {
     s_id[tid] = has_token ? a.ids[(size_t)t * a.K + tid] : -1;
     s_w[tid] = has_token ? a.weights[(size_t)t * a.K + tid] : 0.f;
   }
-  __syncthreads();
 
   // The hidden row is read once and kept in registers for all destinations.
   const int chunks = a.H / 8;  // 16-byte chunks
@@ -50,6 +70,7 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
       if (c < chunks) xv[i] = xr[c];
     }
   }
+  __syncthreads();
 
   for (int d = 0; d < a.R; ++d) {
     if (tid == 0) {
@@ -102,6 +123,12 @@ extern "C" int mf_dispatch_push(const mf_dispatch_args* a, mf_stream_t stream) {
   if (!a || a->C < 1 || a->T > a->C || a->K > mf::kMaxTopK || a->H % 8 != 0 ||
       a->H / 8 > mf::kDispatchThreads * 4 || (a->pitch & 15) != 0 || a->pitch < (long long)a->H * 2 + (2 * a->K + 1) * 4)
     return -1;
-  mf::dispatch_push_kernel<<<a->C, mf::kDispatchThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  size_t smem = 0;
+  if (a->logits != nullptr) {
+    if (a->E < a->K || a->n_group < 1 || a->n_group > 32 || a->E % a->n_group != 0 || !a->route_w || !a->route_ids) return -2;
+    smem = 2 * (size_t)a->E * sizeof(float);
+    if (smem > 40 * 1024) return -3;
+  }
+  mf::dispatch_push_kernel<<<a->C, mf::kDispatchThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
   return (int)cudaGetLastError();
 }

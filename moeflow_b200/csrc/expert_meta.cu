@@ -79,6 +79,9 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   int* warp_sums = offs + L;            // [33]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_dep_launch();
+  for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
+  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
 
   if (a.flags != nullptr && tid < a.R) {
@@ -86,7 +89,6 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   }
   for (int i = tid; i < a.n_counters1; i += kMetaThreads) a.counters1[i] = 0;
   for (int i = tid; i < a.n_counters2; i += kMetaThreads) a.counters2[i] = 0;
-  for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
   __syncthreads();
 
   const int N = a.rows * K;
@@ -199,6 +201,6 @@ extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  mf::expert_meta_kernel<<<1, mf::kMetaThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
-  return (int)cudaGetLastError();
+  return (int)mf::launch_kernel(mf::expert_meta_kernel, dim3(1), dim3(mf::kMetaThreads), smem,
+                                static_cast<cudaStream_t>(stream), true, *a);
 }

@@ -106,6 +106,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above overlaps the tail of the previous kernel.  The gate/up GEMM needs the plan
+  // of the metadata kernel right away, so it waits first and only then lets the next kernel start:
+  // when the down GEMM starts, the plan is therefore complete and it may stream weight tiles while
+  // the gate/up GEMM is still finishing; only its token-operand producers wait for the activations.
+  if (kGateUp) {
+    grid_dep_wait();
+    grid_dep_launch();
+  } else {
+    grid_dep_launch();
+    if (warp >= 2) grid_dep_wait();  // token-operand producers (act rows) and epilogue (arrival counters)
+  }
+
   const int n_tiles = a.plan[MF_PLAN_N_TILES];
   int split = a.plan[a.split_word];
   if (split < 1) split = 1;
@@ -389,8 +401,7 @@ static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStre
   }
   CUtensorMap tm;
   memcpy(&tm, tmap, sizeof(tm));
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tm, *args);
-  return (int)cudaGetLastError();
+  return (int)launch_kernel(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, true, tm, *args);
 }
 
 static int check_args(const mf_gemm_args* a, int n_max, int grid) {

@@ -110,6 +110,15 @@ typedef struct {
   int T, C, H, K, R, L, rank;
   long long pitch;           // bytes per recv row
   int skip_payload;          // 1: hidden lanes are stored only on rows with valid = 1
+  // Optional fused routing: with logits != NULL the kernel routes every token itself (one warp per
+  // token, same arithmetic as mf_router_topk), writes the result to `route_w` / `route_ids` ([T, K]) and
+  // ignores `weights` / `ids`.
+  const float* logits;       // [T, E] fp32
+  const float* bias;         // [E] fp32 or NULL
+  float* route_w;
+  int* route_ids;
+  int E, n_group, topk_group, sigmoid, renorm;
+  float scale;
 } mf_dispatch_args;
 int mf_dispatch_push(const mf_dispatch_args* args, mf_stream_t stream);
 
@@ -188,6 +197,9 @@ int mf_peer_can_access(int dev, int peer_dev, int* ok);
 int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, int R, int rank, unsigned value,
                  int skip_store, unsigned long long* status, unsigned long long wait_ns, mf_stream_t stream);
 const char* mf_error_string(int code);
+// Programmatic dependent launch between the kernels of one forward (default on; MOEFLOW_PDL=0 turns it off).
+int mf_pdl_enabled(void);
+void mf_set_pdl(int on);
 int mf_device_sm_count(int* out);
 
 #ifdef __cplusplus

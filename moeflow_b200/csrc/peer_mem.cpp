@@ -10,6 +10,7 @@
 // (moeflow/fixed.py:234,237; moeflow/comm.py:26-44).  Here NCCL/gloo only carries the handles once.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -96,6 +97,18 @@ int mf_peer_can_access(int dev, int peer_dev, int* ok) {
   }
   return (int)cudaDeviceCanAccessPeer(ok, dev, peer_dev);
 }
+
+static int g_pdl = -1;
+
+int mf_pdl_enabled(void) {
+  if (g_pdl < 0) {
+    const char* v = std::getenv("MOEFLOW_PDL");
+    g_pdl = (v && v[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+
+void mf_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 const char* mf_error_string(int code) {
   if (code < 0) return "moeflow_b200: bad argument";

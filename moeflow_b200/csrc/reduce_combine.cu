@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   const int row = blockIdx.x;  // = s*C + t
   const int s = row / a.C, t = row - s * a.C;
   const int tid = threadIdx.x;
+  grid_dep_launch();
+  grid_dep_wait();  // the down GEMM has completed: y is final
   const int* meta = reinterpret_cast<const int*>(static_cast<const uint8_t*>(a.recv) + (size_t)row * a.pitch +
                                                  (size_t)a.H * 2);
   const bool valid = meta[a.valid_word] != 0;
@@ -55,9 +57,19 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
                                           ((size_t)a.rank * a.C + t) * a.H * 2);
     for (int c = tid; c < chunks; c += kRowThreads) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int k = 0; k < a.K; ++k) {
-        const int p = s_pos[k];
-        if (p >= 0) acc_bf16x8(acc, __ldcg(&y[(size_t)p * chunks + c]));
+      // Issue the loads of up to 8 slots together (they are independent), then add in slot order.
+      for (int k0 = 0; k0 < a.K; k0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int p = (k0 + j < a.K) ? s_pos[k0 + j] : -1;
+          if (p >= 0) v[j] = __ldcg(&y[(size_t)p * chunks + c]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int p = (k0 + j < a.K) ? s_pos[k0 + j] : -1;
+          if (p >= 0) acc_bf16x8(acc, v[j]);
+        }
       }
       dst[c] = pack_bf16x8(acc);
     }
@@ -78,6 +90,7 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
 __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_args a) {
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
+  grid_dep_wait();
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
   if (a.flags != nullptr && tid < a.R) {
     if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);
@@ -90,8 +103,15 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
   for (int c = tid; c < chunks; c += kRowThreads) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (!a.ring) {
-      for (int d = 0; d < a.R; ++d)
-        if (hit[d]) acc_bf16x8(acc, __ldcg(&ret[((size_t)d * a.C + t) * chunks + c]));
+      for (int d0 = 0; d0 < a.R; d0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (d0 + j < a.R && hit[d0 + j]) v[j] = __ldcg(&ret[((size_t)(d0 + j) * a.C + t) * chunks + c]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (d0 + j < a.R && hit[d0 + j]) acc_bf16x8(acc, v[j]);
+      }
     } else {
       for (int step = 1; step <= a.R; ++step) {
         const int d = (a.rank + step) % a.R;
@@ -124,14 +144,14 @@ extern "C" {
 
 int mf_owner_reduce_push(const mf_reduce_push_args* a, mf_stream_t stream) {
   if (!a || a->K > 32 || a->H % 8 != 0 || a->R < 1 || a->C < 1) return -1;
-  mf::owner_reduce_push_kernel<<<a->R * a->C, mf::kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-  return (int)cudaGetLastError();
+  return (int)mf::launch_kernel(mf::owner_reduce_push_kernel, dim3(a->R * a->C), dim3(mf::kRowThreads), 0,
+                                static_cast<cudaStream_t>(stream), true, *a);
 }
 
 int mf_combine(const mf_combine_args* a, mf_stream_t stream) {
   if (!a || a->H % 8 != 0 || a->R < 1 || a->R > mf::kRowThreads || a->C < 1) return -1;
-  mf::combine_kernel<<<a->C, mf::kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-  return (int)cudaGetLastError();
+  return (int)mf::launch_kernel(mf::combine_kernel, dim3(a->C), dim3(mf::kRowThreads), 0,
+                                static_cast<cudaStream_t>(stream), true, *a);
 }
 
 int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, int R, int rank, unsigned value,

@@ -212,7 +212,11 @@ class FixedEPLayer:
         return hit
 
     def stage_pack(self, x, logits, bias, num_valid=None) -> torch.Tensor:
-        """ROUTER + DISPATCH. Returns ``hit [C, R]``."""
+        """ROUTER + DISPATCH. Returns ``hit [C, R]``.  One kernel on the cuda backend."""
+        if self.backend == "cuda":
+            if x.shape[0] > self.C:
+                raise ValueError(f"{x.shape[0]} tokens exceed capacity {self.C}")
+            return self._cuda_dispatch(x, None, None, num_valid, logits=logits, bias=bias)
         weights, ids = self.stage_route(logits, bias)
         return self.stage_dispatch_pack(x, weights, ids, num_valid)
 
@@ -360,10 +364,13 @@ class FixedEPLayer:
         if stop_after is not None and stop_after not in STAGES:
             if not (self.backend == "cuda" and stop_after in CUDA_SUBSTAGES):
                 raise ValueError(f"stop_after must be one of {STAGES}")
-        weights, ids = self.stage_route(logits, bias)
-        if stop_after == "ROUTER":
-            return weights
-        hit = self.stage_dispatch_pack(x, weights, ids, num_valid)
+        if self.backend == "cuda" and stop_after != "ROUTER":
+            hit = self.stage_pack(x, logits, bias, num_valid)  # routing fused into the dispatch kernel
+        else:
+            weights, ids = self.stage_route(logits, bias)
+            if stop_after == "ROUTER":
+                return weights
+            hit = self.stage_dispatch_pack(x, weights, ids, num_valid)
         if stop_after == "DISPATCH":
             return hit
         if self.backend == "torch":
@@ -447,7 +454,12 @@ class FixedEPLayer:
             peer_recv=self._peer_recv.data_ptr(), peer_flag=self._peer_dflag.data_ptr(), hit=self.hit.data_ptr(),
             epoch=self._epoch.data_ptr(), done_counter=self._done[0:].data_ptr(), T=0, C=Cc, H=H, K=K, R=R, L=L,
             rank=self.rank, pitch=self.pitch * 2, skip_payload=int(self.gemm_kwargs.get("skip_payload", 1)),
+            route_w=self._route_w.data_ptr(), route_ids=self._route_ids.data_ptr(), E=cfg.n_routed_experts,
+            n_group=cfg.n_group, topk_group=cfg.topk_group, sigmoid=int(cfg.scoring_func == "sigmoid"),
+            renorm=int(cfg.norm_topk_prob), scale=float(cfg.routed_scaling_factor),
         )
+        if cfg.scoring_func not in ("sigmoid", "softmax"):
+            raise ValueError(f"unknown scoring function {cfg.scoring_func!r}")
         self._a_meta = S.MetaArgs(
             recv=self._recv_store.data_ptr(), pitch=self.pitch * 2, H=H, K=K, L=L, rows=R * Cc, R=R,
             flags=self._disp_flags.data_ptr(), epoch=self._epoch.data_ptr(), offsets=self.offsets.data_ptr(),
@@ -530,20 +542,30 @@ class FixedEPLayer:
             return
         self.w13, self.w2, self._tmap13, self._tmap2 = w13_local, w2_local, tmap13, tmap2
 
-    def _cuda_dispatch(self, x, weights, ids, num_valid) -> torch.Tensor:
+    def _cuda_dispatch(self, x, weights, ids, num_valid, logits=None, bias=None) -> torch.Tensor:
         from .ops import _lib
 
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise ValueError("x must be contiguous bf16")
-        if ids.dtype != torch.int32:
-            ids = ids.to(torch.int32)
-        weights = weights.to(torch.float32).contiguous()
-        ids = ids.contiguous()
         a = self._a_dispatch
-        a.x, a.weights, a.ids = x.data_ptr(), weights.data_ptr(), ids.data_ptr()
+        if logits is not None:
+            if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.shape[1] != self.cfg.n_routed_experts:
+                raise ValueError("logits must be contiguous fp32 [T, E]")
+            if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous()):
+                raise ValueError("bias must be contiguous fp32 [E]")
+            a.logits, a.bias = logits.data_ptr(), None if bias is None else bias.data_ptr()
+            a.weights = a.ids = None
+        else:
+            if ids.dtype != torch.int32:
+                ids = ids.to(torch.int32)
+            weights = weights.to(torch.float32).contiguous()
+            ids = ids.contiguous()
+            a.logits = a.bias = None
+            a.weights, a.ids = weights.data_ptr(), ids.data_ptr()
+        a.x = x.data_ptr()
         a.num_valid = None if num_valid is None else num_valid.data_ptr()
         a.T = x.shape[0]
-        self._keep = [x, weights, ids, num_valid]
+        self._keep = [x, weights, ids, num_valid, logits, bias]
         _lib.check(self._lib.mf_dispatch_push(C.byref(a), _lib.stream_ptr()), "dispatch_push")
         return self.hit
 

@@ -79,6 +79,16 @@ class DispatchArgs(C.Structure):
         ("rank", C.c_int),
         ("pitch", C.c_longlong),
         ("skip_payload", C.c_int),
+        ("logits", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("route_w", C.c_void_p),
+        ("route_ids", C.c_void_p),
+        ("E", C.c_int),
+        ("n_group", C.c_int),
+        ("topk_group", C.c_int),
+        ("sigmoid", C.c_int),
+        ("renorm", C.c_int),
+        ("scale", C.c_float),
     ]
 
 
@@ -202,6 +212,10 @@ def lib() -> C.CDLL:
         fn = getattr(handle, name)
         fn.argtypes = argtypes
         fn.restype = I
+    handle.mf_set_pdl.argtypes = [I]
+    handle.mf_set_pdl.restype = None
+    handle.mf_pdl_enabled.argtypes = []
+    handle.mf_pdl_enabled.restype = I
     handle.mf_error_string.argtypes = [I]
     handle.mf_error_string.restype = C.c_char_p
     return handle
