@@ -45,15 +45,23 @@ def main() -> None:
     ap.add_argument("--backend", default="cuda", choices=["cuda", "torch"])
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--small", action="store_true", help="small layer shape (smoke runs)")
+    ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (keeps hidden/intermediate)")
+    ap.add_argument("--only-full", action="store_true", help="time only the whole layer (profiling runs)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     info = init_dist()
     cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=32, top_k=4) if args.small else GLM53_FLASH_I1536
+    if args.experts is not None:
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, n_routed_experts=args.experts)
     w13, w2 = _weights(cfg, info.rank, info.world, info.device)
     bias = make_bias(cfg, 1, device=info.device)
     flush = None if args.no_flush else L2Flush(device=info.device)
     stages = list(STAGES)
-    if args.backend == "cuda":
+    if args.only_full:
+        stages = ["COMBINE"]
+    elif args.backend == "cuda":
         at = stages.index("EXPERT")
         stages = stages[:at] + list(CUDA_SUBSTAGES) + stages[at:]
     points = []
@@ -80,7 +88,7 @@ def main() -> None:
         status = layer.check_status() if args.backend == "cuda" else {"code": 0}
         points.append({"tokens": T, "prefix_us": prefix_us, "stage_us": stage_us, "padding": pad, "status": status})
         if info.rank == 0:
-            print(f"T={T}: " + "  ".join(f"{k}={v:.1f}" for k, v in stage_us.items()) + f"  | full {prefix_us['COMBINE']:.1f} us, one valid row {pad['valid_1']:.1f} us")
+            print(f"T={T}: " + "  ".join(f"{k}={v:.1f}" for k, v in stage_us.items()) + f"  | full {prefix_us['COMBINE']:.1f} us, one valid row {pad['valid_1']:.1f} us", flush=True)
         del layer
         torch.cuda.synchronize()
     if info.rank == 0 and args.out:
