@@ -12,7 +12,7 @@ import platform
 import socket
 import subprocess
 import sys
-from importlib import import_module
+from importlib import import_module, metadata
 from pathlib import Path
 
 REPO = Path(__file__).resolve().parents[2]
@@ -30,8 +30,13 @@ def git_info(repo: Path = REPO) -> dict:
 
 
 def _version(module: str):
+    """Installed version without importing the package (importing an inference engine takes seconds)."""
     try:
-        return getattr(import_module(module), "__version__", None)
+        return metadata.version(module)
+    except metadata.PackageNotFoundError:
+        pass
+    try:
+        return getattr(import_module(module), "__version__", None) if module == "moeflow_b200" else None
     except Exception:
         return None
 

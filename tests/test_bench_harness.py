@@ -1,0 +1,161 @@
+"""Statistics, decision rule, records, validation gates, serving validators, report generators."""
+
+import json
+import math
+
+import pytest
+import torch
+
+from moeflow_b200.bench.logits import compare_logits, parse_raw_logits
+from moeflow_b200.bench.record import make_record, write_record
+from moeflow_b200.bench.stats import paired_ab, percentile, summarize, t95
+from moeflow_b200.bench.validation import check_backend_pair, check_reference, require_matching_variants
+from moeflow_b200.cli import summarize as S
+from moeflow_b200.cli.smoke_client import compare, has_complete_logprobs, validate_prompts
+from moeflow_b200.cli.validate_serving_result import METRICS, validate_result
+
+
+def test_student_t_values():
+    for df, want in ((1, 12.706), (2, 4.303), (9, 2.262), (19, 2.093), (30, 2.042)):
+        assert abs(t95(df) - want) < 2e-3
+    assert abs(t95(1000) - 1.962) < 2e-3
+    with pytest.raises(ValueError):
+        t95(0)
+
+
+def test_percentile_and_summary():
+    xs = [4.0, 1.0, 3.0, 2.0]
+    assert percentile(xs, 0) == 1.0 and percentile(xs, 100) == 4.0 and percentile(xs, 50) == 2.5
+    s = summarize(xs)
+    assert s.n == 4 and s.median == 2.5 and s.min == 1.0 and abs(s.p95 - 3.85) < 1e-12
+    assert summarize([7.0]).std == 0.0
+    with pytest.raises(ValueError):
+        percentile([], 50)
+
+
+def test_paired_rule_needs_both_conditions():
+    a = [100.0, 101.0, 99.5, 100.5, 100.2, 99.8]
+    faster = [x - 5.0 for x in a]
+    r = paired_ab(a, faster)
+    assert r.significant and r.beneficial and r.mean_diff < 0 and r.ci95[1] < 0
+    slower = paired_ab(faster, a)
+    assert slower.significant and not slower.beneficial
+    # a consistent but tiny gain does not beat the per-arm noise
+    tiny = paired_ab(a, [x - 0.01 for x in a])
+    assert not tiny.significant
+    noisy_a = [100.0, 120.0, 80.0, 110.0, 90.0]
+    noisy_b = [95.0, 118.0, 85.0, 100.0, 97.0]
+    assert not paired_ab(noisy_a, noisy_b).significant
+    with pytest.raises(ValueError):
+        paired_ab([1.0], [1.0])
+
+
+def test_records_are_self_describing_and_atomic(tmp_path):
+    rec = make_record("unit", {"x": 1}, {"y": 2}, seed=3, complete=False)
+    assert {"kind", "created", "complete", "git", "env", "seed", "command", "config", "results"} <= set(rec)
+    assert "torch" in rec["env"] and "sha" in rec["git"]
+    path = write_record(tmp_path / "deep" / "r.json", rec)
+    assert json.loads(path.read_text())["complete"] is False and not list(path.parent.glob("*.tmp"))
+
+
+def test_gates_reject_signed_zero_nan_and_errors():
+    pos, neg = torch.tensor([[0.0]]), torch.tensor([[-0.0]])
+    assert not check_backend_pair(pos, neg, pos)["bitwise_equal"]
+    with pytest.raises(RuntimeError, match="outputs differ"):
+        require_matching_variants(pos, neg)
+    nan = torch.tensor([float("nan")])
+    with pytest.raises(RuntimeError, match="outputs differ"):
+        require_matching_variants(nan, nan.clone())
+    require_matching_variants(torch.ones(3), torch.ones(3))
+    ref = torch.randn(4, 8, generator=torch.Generator().manual_seed(0))
+    good = check_reference(ref + 1e-4, ref)
+    assert good["passed"] and good["tokens_checked"] == 4
+    assert not check_reference(ref * 1.5, ref)["passed"]
+    assert not check_reference(torch.full_like(ref, float("inf")), ref)["passed"]
+    assert check_reference(ref[:0], ref[:0])["passed"]
+
+
+def _serving_record(n=4, inp=8, outp=4, conc=2, duration=2.0):
+    rec = {"num_prompts": n, "completed": n, "failed": 0, "max_concurrency": conc, "total_input_tokens": n * inp,
+           "total_output_tokens": n * outp, "input_lens": [inp] * n, "output_lens": [outp] * n, "errors": [""] * n,
+           "ttfts": [0.1] * n, "latencies": [0.5] * n, "itls": [[0.01] * (outp - 1)] * n, "duration": duration,
+           "request_throughput": n / duration, "output_throughput": n * outp / duration}
+    rec.update({m: 1.0 for m in METRICS})
+    return rec
+
+
+def test_serving_result_validator():
+    ok = validate_result(_serving_record(), 4, 8, 4, 2)
+    assert ok["passed"] and ok["total_output_tokens"] == 16 and ok["tokens_per_second"] == 8.0
+    for mutate in (
+        lambda r: r.update(completed=3),
+        lambda r: r.update(output_lens=[4, 4, 4, 3]),
+        lambda r: r.update(errors=["", "", "", "timeout"]),
+        lambda r: r.update(median_tpot_ms=float("nan")),
+        lambda r: r.pop("p99_itl_ms"),
+        lambda r: r.update(itls=[[0.01]] * 3),
+        lambda r: r.update(output_throughput=1.0),
+        lambda r: r.update(ttfts=[0.1, 0.1, 0.1, -1.0]),
+    ):
+        rec = _serving_record()
+        mutate(rec)
+        with pytest.raises(ValueError):
+            validate_result(rec, 4, 8, 4, 2)
+    with pytest.raises(ValueError):
+        validate_result(_serving_record(), 4, 8, 1, 2)
+
+
+def test_smoke_client_validation_and_compare():
+    assert validate_prompts(["a", [1, 2]]) == ["a", [1, 2]]
+    for bad in ([], "x", [""], [[]], [[1, -2]], [[1.5]], [None]):
+        with pytest.raises(ValueError):
+            validate_prompts(bad)
+    rec = {"prompt": "p", "dp_rank": 0, "text": "t", "tokens": ["a", "b"], "logprobs": [-0.1, -0.2], "complete": True}
+    assert has_complete_logprobs(rec) and not has_complete_logprobs({**rec, "logprobs": [-0.1]})
+    assert not has_complete_logprobs({**rec, "logprobs": [-0.1, math.inf]})
+    a = {"records": [rec]}
+    assert compare(a, {"records": [dict(rec)]})["passed"]
+    assert not compare(a, {"records": [{**rec, "tokens": ["a", "c"]}]})["passed"]
+    assert compare(a, {"records": [{**rec, "logprobs": [-0.1, -0.25]}]})["passed"]
+    assert not compare(a, {"records": [{**rec, "logprobs": [-0.1, -0.25]}]}, exact_logprobs=True)["passed"]
+    assert not compare(a, {"records": [{**rec, "complete": False}]})["passed"]
+    assert not compare(a, {"records": []})["passed"]
+
+
+def test_raw_logits_are_parsed_strictly():
+    arr = parse_raw_logits([[0.5, 1.5, -2.0], [1.0, 2.0, 3.0]], 3)
+    assert arr.shape == (2, 3) and arr.dtype.name == "float32"
+    assert parse_raw_logits([0.5, 1.5, -2.0], 3).shape == (1, 3)
+    with pytest.raises(ValueError):
+        parse_raw_logits([[0.5, 1.5]], 3)
+    with pytest.raises(ValueError):
+        parse_raw_logits([[0.5, float("nan"), 1.0]], 3)
+    same = compare_logits(arr, arr.copy())
+    assert same["bitwise_equal"] and same["sha256_a"] == same["sha256_b"]
+    other = arr.copy()
+    other[0, 0] = -0.0 + 0.5000001
+    assert not compare_logits(arr, other)["bitwise_equal"]
+    assert not compare_logits(arr, arr[:1])["bitwise_equal"]
+
+
+def test_report_generators_refuse_bad_records(tmp_path):
+    pt = {"tokens": 8, "passed": True, "reference": [{"normwise_rel_err": 1e-3}],
+          "graph_us": {"median": 10.0, "p95": 11.0}, "eager_us": {"median": 30.0}}
+    rec = make_record("bench_layer", {"backend": "fused", "world": 2}, {"points": [pt]})
+    good = write_record(tmp_path / "good.json", rec)
+    assert "| fused | 2 | 8 | 10.0 | 11.0 | 30.0 |" in S.layer_table([str(good)])
+    bad = write_record(tmp_path / "bad.json", {**rec, "complete": False})
+    with pytest.raises(SystemExit):
+        S.layer_table([str(bad)])
+    failed = write_record(tmp_path / "failed.json", make_record("bench_layer", {"backend": "fused", "world": 2}, {"points": [{**pt, "passed": False}]}))
+    with pytest.raises(SystemExit):
+        S.layer_table([str(failed)])
+    with pytest.raises(SystemExit):
+        S.ab_table([str(good)])  # wrong kind
+    csv_path = tmp_path / "launches.csv"
+    csv_path.write_text('==PROF== header\n"ID","Kernel Name","Metric Name","Metric Unit","Metric Value"\n'
+                        '"0","mf::combine_kernel(mf_combine_args)","gpu__time_duration.sum","ns","2,000"\n'
+                        '"1","mf::combine_kernel(mf_combine_args)","gpu__time_duration.sum","ns","3,000"\n'
+                        '"2","void at::native::fill(int)","gpu__time_duration.sum","ns","1,000"\n')
+    text = S.launches_summary(str(csv_path))
+    assert "mf::combine_kernel | 2 | 1.00 | 5.0" in text and "library helper kernels (at::native): 1" in text
