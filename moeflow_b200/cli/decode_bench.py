@@ -1,0 +1,81 @@
+"""Decode throughput of the GLM-5.3-Flash-shaped model: time per output token and tokens per second.
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m moeflow_b200.cli.decode_bench \
+        --layers 42 --concurrency 64 --input-len 1024 --output-len 1024 --out results/decode_c64.json
+
+DP = EP = N: the ``concurrency`` sequences are spread over the ranks (each rank decodes
+``concurrency / N`` sequences per step), every layer's experts are sharded over the ranks, attention runs
+per rank (TP=1).  Weights are random-initialised at the named shape, token inputs are synthetic; a
+stand-in prefill fills the KV cache for ``input-len`` positions, then ``output-len`` decode steps are
+replayed from one CUDA graph per step and timed on the device (barrier-aligned, max over ranks).
+
+TPOT = time of one decode step; tokens/s = concurrency / TPOT.
+"""
+
+from __future__ import annotations
+
+import argparse
+import dataclasses
+
+import torch
+import torch.distributed as dist
+
+from ..bench.backends import init_dist
+from ..bench.record import make_record, write_record
+from ..bench.stats import summarize
+from ..bench.timing import aligned_start, max_over_ranks
+from ..config import GLM53_FLASH_I1536
+from ..models.glm_moe import AttentionConfig, DecodeModel
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=42)
+    ap.add_argument("--concurrency", type=int, default=4)
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=1024)
+    ap.add_argument("--intermediate", type=int, default=1536)
+    ap.add_argument("--chunk", type=int, default=64, help="decode steps per timing sample")
+    ap.add_argument("--no-attention", action="store_true")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    info = init_dist()
+    cfg = dataclasses.replace(GLM53_FLASH_I1536, moe_intermediate_size=args.intermediate)
+    batch = max(1, (args.concurrency + info.world - 1) // info.world)
+    acfg = AttentionConfig(max_seq=args.input_len + args.output_len + 8)
+    model = DecodeModel(cfg, info.rank, info.world, batch, args.layers, info.device, acfg, attention=not args.no_attention)
+    model.prefill_standin(args.input_len)
+    model.x.copy_(torch.randn(batch, cfg.hidden_size, device=info.device).bfloat16())
+    model.capture()
+    for _ in range(3):
+        model.step()
+    samples = []
+    done = 0
+    while done < args.output_len:
+        n = min(args.chunk, args.output_len - done)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        aligned_start()
+        start.record()
+        for _ in range(n):
+            model.step()
+        end.record()
+        end.synchronize()
+        samples.append(max_over_ranks(start.elapsed_time(end) / n))
+        done += n
+    status = model.routed.check_status()
+    tpot = summarize(samples)
+    result = {"tpot_ms": tpot.to_dict(), "tokens_per_second": args.concurrency / (tpot.median / 1e3), "batch_per_rank": batch,
+              "status": status, "finite": bool(torch.isfinite(model.out.float()).all())}
+    if info.rank == 0:
+        print(f"layers={args.layers} EP={info.world} concurrency={args.concurrency}: TPOT median {tpot.median:.3f} ms "
+              f"(p95 {tpot.p95:.3f}), {result['tokens_per_second']:.1f} tokens/s, status {status['name']}", flush=True)
+        if args.out:
+            write_record(args.out, make_record("decode_bench", {**vars(args), "world": info.world, "cfg": cfg.to_dict()}, result))
+    model.close()
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -287,7 +287,8 @@ class FixedEPLayer:
         L, K = self.L, self.K
         keys = torch.where(local >= 0, local, L).reshape(-1)
         order = torch.sort(keys, stable=True).indices
-        counts = torch.bincount(keys, minlength=L + 1)
+        # scatter_add instead of bincount: no host round trip, so the twin can be captured in a graph too
+        counts = torch.zeros(L + 1, dtype=torch.int64, device=keys.device).scatter_add_(0, keys, torch.ones_like(keys))
         offsets = torch.zeros(L + 1, dtype=torch.int64, device=keys.device)
         torch.cumsum(counts[:L], dim=0, out=offsets[1:])
         inv = torch.empty_like(order)

@@ -1,0 +1,50 @@
+"""Shared expert, MoE block and the decode model on one GPU at small shapes."""
+
+import pytest
+import torch
+
+from moeflow_b200 import MoEConfig
+from moeflow_b200.experts import swiglu_clamp
+from moeflow_b200.tolerances import normwise_rel_err
+
+pytestmark = pytest.mark.gpu
+
+CFG = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=16, n_shared_experts=1, top_k=4)
+
+
+@pytest.mark.parametrize("capacity,tokens", [(8, 5), (128, 128)])
+def test_shared_expert_matches_fp32(capacity, tokens):
+    from moeflow_b200.models.glm_moe import SharedExpert
+
+    g = torch.Generator().manual_seed(0)
+    w13 = (torch.randn(512, 512, generator=g) * 2 / 512**0.5).bfloat16().cuda()
+    w2 = (torch.randn(512, 256, generator=g) / 16).bfloat16().cuda()
+    x = torch.randn(tokens, 512, generator=g).bfloat16().cuda()
+    shared = SharedExpert(w13, w2, capacity, 10.0)
+    out = shared(x).clone()
+    torch.cuda.synchronize()
+    assert int(shared.status.item()) == 0
+    ref = swiglu_clamp(x.float() @ w13.float().t(), 10.0) @ w2.float().t()
+    assert normwise_rel_err(out, ref) < 4 * 2.0**-8
+
+
+def test_decode_model_steps_and_matches_eager():
+    from moeflow_b200.models.glm_moe import AttentionConfig, DecodeModel
+
+    model = DecodeModel(CFG, 0, 1, batch=4, n_layers=3, device="cuda", acfg=AttentionConfig(n_heads=8, n_kv_heads=2, head_dim=64, max_seq=64))
+    model.prefill_standin(16)
+    model.x.copy_(torch.randn(4, CFG.hidden_size, generator=torch.Generator().manual_seed(1)).bfloat16())
+    eager = model.step().clone()
+    assert int(model.pos) == 17 and torch.isfinite(eager.float()).all()
+    # replay the same step from a graph: same position and cache contents give the same numbers
+    model.prefill_standin(16)
+    model.capture()
+    model.prefill_standin(16)
+    replay = model.step().clone()
+    torch.cuda.synchronize()
+    assert model.routed.check_status()["code"] == 0
+    assert normwise_rel_err(replay, eager.float()) < 1e-2
+    for _ in range(5):
+        out = model.step()
+    assert int(model.pos) == 22 and torch.isfinite(out.float()).all()
+    model.close()
