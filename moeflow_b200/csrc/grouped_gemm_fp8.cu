@@ -1,0 +1,489 @@
+// Block-scaled FP8 (e4m3) grouped expert GEMMs on tcgen05, and the 1x128 activation quantiser.
+//
+// Checkpoint format: weights are float8_e4m3fn with one fp32 scale per 128x128 block
+// (weight_scale_inv); activations are quantised on the fly to e4m3 with one fp32 scale per row and
+// 128-wide K group.  These scales are arbitrary fp32 numbers, not the power-of-two per-32 scales the
+// hardware block-scaling mode wants, so the kernel accumulates in two levels:
+//
+//   per 128-wide K block:  tmp[128, n]  = W_q[128 rows, 128 k] . X_q[n, 128 k]^T      (tcgen05 kind::f8f6f4,
+//                                                                                     fp32 in tensor memory)
+//                          acc[r, n]   += w_scale[block(r), kb] * x_scale[n, kb] * tmp[r, n]     (registers)
+//
+// The weight block of a unit (128 rows) is exactly one scale-block row, and one K block of 128 bytes is
+// one TMA box row and one scale-block column, so a unit needs one weight scale per K block (two for
+// gate/up) and one activation scale per token and K block; the epilogue warps preload them into
+// shared memory per unit.  Tensor-memory accumulators are double-buffered per K block so that the
+// promotion of block kb overlaps the MMAs of block kb+1.
+//
+// Everything else (swap-AB, persistent CTAs, device-side plan, split-K with ordered fix-up, bounded
+// waits, warp roles) is as in grouped_gemm_tc.cu.  Output is bf16: SwiGLU activations for gate/up,
+// routing-weighted rows for the down projection.
+//
+// The reference has no FP8 kernel of its own: it dequantises to bf16 (moeflow/weights.py:23-27) or calls
+// the serving engine's fused experts and moe_kernel_quantize_input (moeflow/integrations/vllm_pf.py:97).
+#include <cuda.h>
+#include <cuda_fp8.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "moeflow_b200.h"
+
+namespace mf {
+
+constexpr int kF8BlockM = 128;
+constexpr int kF8TileA = 128 * 128;
+constexpr int kF8Threads = 256;
+constexpr int kF8Gather = 64;
+constexpr int kF8TmpStages = 2;
+constexpr int kF8MaxKb = 32;  // K <= 4096 (one unit never spans more K blocks than this)
+
+template <bool kGateUp, int N_MAX>
+struct F8Cfg {
+  static constexpr int kATiles = kGateUp ? 2 : 1;
+  static constexpr int kStageA = kATiles * kF8TileA;
+  static constexpr int kStageB = N_MAX * 128;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kTableBytes = 2 * (N_MAX * kF8MaxKb + 2 * kF8MaxKb) * 4;  // two unit parities
+  static constexpr int kStages = (200 * 1024 - kTableBytes) / kStageBytes > 8 ? 8 : (200 * 1024 - kTableBytes) / kStageBytes;
+  static constexpr int kTmpCols = kATiles * N_MAX;
+  static constexpr int kTmemCols = kF8TmpStages * kTmpCols;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kTableBytes + 1024 + 256;
+};
+
+struct F8Pipe {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int n) {
+    if (++stage == n) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+template <bool kGateUp, int N_MAX>
+__global__ void __launch_bounds__(kF8Threads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_args a) {
+  using Cfg = F8Cfg<kGateUp, N_MAX>;
+  constexpr int STAGES = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * Cfg::kStageA;
+  float* sTable = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);  // [2][N_MAX*kMaxKb + 2*kMaxKb]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes + Cfg::kTableBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmp_full = bars + 2 * STAGES;
+  uint64_t* tmp_empty = tmp_full + kF8TmpStages;
+  uint64_t* tbl_bar = tmp_empty + kF8TmpStages;  // [2] one per unit parity
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1 + kF8Gather);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < kF8TmpStages; ++s) {
+      mbar_init(&tmp_full[s], 1);
+      mbar_init(&tmp_empty[s], 4);
+    }
+    mbar_init(&tbl_bar[0], 4);
+    mbar_init(&tbl_bar[1], 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  grid_dep_wait();
+  grid_dep_launch();
+
+  const int n_tiles = a.plan[MF_PLAN_N_TILES];
+  int split = a.plan[a.split_word];
+  if (split < 1) split = 1;
+  const int kb_per = a.k_blocks / split;
+  const int total_units = n_tiles * a.m_blocks * split;
+  const unsigned long long wait_ns = a.wait_ns;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- weight TMA producer
+    F8Pipe st;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
+      const int row0 = a.tile_e[tt] * a.rows_per_expert + mb * kF8BlockM;
+      for (int j = 0; j < kb_per; ++j) {
+        const int kb = ks * kb_per + j;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns));
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 0, blockIdx.x, 0);
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageA);
+          uint8_t* dst = sA + st.stage * Cfg::kStageA;
+          tma_load_2d(dst, &tmap_w, &full_bar[st.stage], kb * 128, row0);
+          if (kGateUp) tma_load_2d(dst + kF8TileA, &tmap_w, &full_bar[st.stage], kb * 128, row0 + a.up_row_offset);
+        }
+        __syncwarp();
+        st.advance(STAGES);
+      }
+    }
+    if (!ok) {
+      const unsigned long long t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 100000ull) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- UMMA issuer (one K block per tmp stage)
+    F8Pipe st, tmp;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt];
+      uint32_t n_tile = (uint32_t)((n_rows + 15) & ~15);
+      if (n_tile < 16) n_tile = 16;
+      const uint32_t idesc = umma_idesc(0, 0, kF8BlockM, n_tile);  // e4m3 x e4m3 -> fp32
+      for (int j = 0; j < kb_per; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_empty[tmp.stage], tmp.phase ^ 1u, abort_flag, wait_ns));
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmAccTimeout, 1, blockIdx.x, 0);
+          break;
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full_bar[st.stage], st.phase, abort_flag, wait_ns));
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmFullTimeout, 1, blockIdx.x, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          const uint32_t d0 = tmem_base + tmp.stage * Cfg::kTmpCols;
+          const uint32_t a_addr = smem_u32(sA + st.stage * Cfg::kStageA);
+          const uint32_t b_addr = smem_u32(sB + st.stage * Cfg::kStageB);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t bdesc = umma_desc_sw128(b_addr + k * 32);
+            umma_f8(d0, umma_desc_sw128(a_addr + k * 32), bdesc, idesc, k > 0 ? 1u : 0u);
+            if (kGateUp) umma_f8(d0 + N_MAX, umma_desc_sw128(a_addr + kF8TileA + k * 32), bdesc, idesc, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[st.stage]);
+          umma_commit(&tmp_full[tmp.stage]);
+        }
+        __syncwarp();
+        st.advance(STAGES);
+        tmp.advance(kF8TmpStages);
+      }
+    }
+  } else if (warp < 4) {
+    // ---------------------------------------------------------------- token-operand producers (e4m3 rows)
+    const int gt = tid - 64, r_in = gt >> 3, chunk = gt & 7;
+    const uint32_t sw_off = (uint32_t)((chunk ^ r_in) << 4);
+    F8Pipe st;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const int ks = u % split, tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt];
+      int n_tile = (n_rows + 15) & ~15;
+      if (n_tile < 16) n_tile = 16;
+      const uint8_t* rp[N_MAX / 8];
+#pragma unroll
+      for (int i = 0; i < N_MAX / 8; ++i) {
+        const int n = r_in + 8 * i;
+        rp[i] = nullptr;
+        if (n < n_rows) {
+          const long long idx = a.b_index ? (long long)a.b_index[row_start + n] : (long long)(row_start + n);
+          rp[i] = static_cast<const uint8_t*>(a.b_base) + idx * a.b_pitch + chunk * 16;
+        }
+      }
+      for (int j = 0; j < kb_per; ++j) {
+        const int kb = ks * kb_per + j;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns));
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 2, blockIdx.x, 0);
+          break;
+        }
+        const uint32_t b_stage = smem_u32(sB + st.stage * Cfg::kStageB);
+#pragma unroll
+        for (int i = 0; i < N_MAX / 8; ++i) {
+          const int n = r_in + 8 * i;
+          if (n < n_tile) {
+            const bool live = rp[i] != nullptr;
+            cp_async_16(b_stage + n * 128 + sw_off, live ? (const void*)(rp[i] + (long long)kb * 128) : a.b_base, live ? 16u : 0u);
+          }
+        }
+        cp_async_mbar_arrive_noinc(&full_bar[st.stage]);
+        st.advance(STAGES);
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else {
+    // ---------------------------------------------------------------- promotion + epilogue
+    const int wq = warp & 3, row = wq * 32 + lane;
+    F8Pipe tmp;
+    bool ok = true;
+    uint32_t unit_parity = 0;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, unit_parity ^= 1u) {
+      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt], e = a.tile_e[tt];
+      int n_tile = (n_rows + 15) & ~15;
+      if (n_tile < 16) n_tile = 16;
+      const int kb0 = ks * kb_per;
+
+      // scale table of this unit: x scales [n][j] and weight scales [t][j], j = kb - kb0
+      float* tbl = sTable + unit_parity * (N_MAX * kF8MaxKb + 2 * kF8MaxKb);
+      float* tblW = tbl + N_MAX * kF8MaxKb;
+      const int row_blocks = a.rows_per_expert / kF8BlockM;
+      for (int n = wq; n < n_tile; n += 4) {
+        float v = 0.f;
+        const bool live = n < n_rows;
+        long long idx = 0;
+        if (live) idx = a.b_index ? (long long)a.b_index[row_start + n] : (long long)(row_start + n);
+        for (int j = lane; j < kb_per; j += 32) {
+          v = live ? a.b_scale[idx * a.b_scale_pitch + kb0 + j] : 0.f;
+          tbl[n * kF8MaxKb + j] = v;
+        }
+      }
+      if (wq < (kGateUp ? 2 : 1)) {
+        const int rb = (wq == 0 ? 0 : a.up_row_offset / kF8BlockM) + mb;
+        const float* ws = a.w_scale + ((long long)e * row_blocks + rb) * a.k_blocks + kb0;
+        for (int j = lane; j < kb_per; j += 32) tblW[wq * kF8MaxKb + j] = ws[j];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tbl_bar[unit_parity]);
+      // every second unit reuses a barrier: its phase is (number of earlier units with this parity) & 1
+      const uint32_t tbl_phase = (uint32_t)(((u - blockIdx.x) / gridDim.x) >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_bar[unit_parity], tbl_phase, abort_flag, wait_ns));
+      if (!ok) {
+        if (lane == 0) report_status(a.status, kGemmAccTimeout, 4, blockIdx.x, 0);
+        break;
+      }
+
+      float acc_g[N_MAX], acc_u[kGateUp ? N_MAX : 1];
+#pragma unroll
+      for (int i = 0; i < N_MAX; ++i) acc_g[i] = 0.f;
+      if (kGateUp) {
+#pragma unroll
+        for (int i = 0; i < N_MAX; ++i) acc_u[i] = 0.f;
+      }
+
+      for (int j = 0; j < kb_per; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_full[tmp.stage], tmp.phase, abort_flag, wait_ns));
+        if (!ok) {
+          if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + tmp.stage * Cfg::kTmpCols;
+        const float wsg = tblW[j];
+        const float wsu = kGateUp ? tblW[kF8MaxKb + j] : 0.f;
+#pragma unroll
+        for (int c0 = 0; c0 < N_MAX; c0 += 16) {
+          if (c0 < n_tile) {
+            uint32_t g[16], up[16];
+            tmem_ld_16(taddr + c0, g);
+            if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float xs = tbl[(c0 + i) * kF8MaxKb + j];
+              acc_g[c0 + i] = fmaf(__uint_as_float(g[i]), wsg * xs, acc_g[c0 + i]);
+              if (kGateUp) acc_u[c0 + i] = fmaf(__uint_as_float(up[i]), wsu * xs, acc_u[c0 + i]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmp_empty[tmp.stage]);
+        tmp.advance(kF8TmpStages);
+      }
+      if (!ok) break;
+
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
+      const long long out_col = (long long)mb * kF8BlockM + row;
+      if (split == 1) {
+#pragma unroll
+        for (int n = 0; n < N_MAX; ++n) {
+          if (n < n_rows) {
+            float v = acc_g[n];
+            if (kGateUp) {
+              float w = acc_u[n];
+              if (a.round_h) {
+                v = bf16_round(v);
+                w = bf16_round(w);
+              }
+              v = swiglu_clamped(v, w, a.limit);
+            } else if (a.row_scale) {
+              v *= a.row_scale[row_start + n];
+            }
+            out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+          }
+        }
+      } else {
+        const int tile_mb = tt * a.m_blocks + mb;
+        const long long slot_floats = (long long)Cfg::kATiles * N_MAX * kF8BlockM;
+        float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
+#pragma unroll
+        for (int n = 0; n < N_MAX; ++n) {
+          if (n < n_rows) {
+            __stcg(&mine[(long long)n * kF8BlockM + row], acc_g[n]);
+            if (kGateUp) __stcg(&mine[(long long)(N_MAX + n) * kF8BlockM + row], acc_u[n]);
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(&a.counters[tile_mb * 4 + wq], 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == split - 1) {
+          __threadfence();
+          const float* base = a.partial + (long long)tile_mb * split * slot_floats;
+          for (int n = 0; n < n_rows; ++n) {
+            float v = 0.f, w = 0.f;
+            for (int s = 0; s < split; ++s) {
+              const float* p = base + s * slot_floats;
+              v += __ldcg(&p[(long long)n * kF8BlockM + row]);
+              if (kGateUp) w += __ldcg(&p[(long long)(N_MAX + n) * kF8BlockM + row]);
+            }
+            if (kGateUp) {
+              if (a.round_h) {
+                v = bf16_round(v);
+                w = bf16_round(w);
+              }
+              v = swiglu_clamped(v, w, a.limit);
+            } else if (a.row_scale) {
+              v *= a.row_scale[row_start + n];
+            }
+            out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+          }
+          if (lane == 0) a.counters[tile_mb * 4 + wq] = 0;
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// -------------------------------------------------------------------------------------------------
+// 1x128 activation quantisation: x[row, :] (bf16) -> q[row, :] (e4m3) and scales[row, g] = amax_g / 448.
+// One CTA per output row; 16 threads share a 128-wide group.  Rows can be gathered (row_index), skipped
+// when an int32 flag inside the source row is zero (valid_off >= 0: the received-row valid flag), and
+// bounded by a device-side row count (n_rows_dev, e.g. the plan's entry count).
+// -------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const uint8_t* __restrict__ x, long long x_pitch, const int* __restrict__ row_index, int hidden,
+                  uint8_t* __restrict__ q, float* __restrict__ scales, long long valid_off, const int* n_rows_dev) {
+  grid_dep_launch();
+  grid_dep_wait();
+  const int r = blockIdx.x;
+  if (n_rows_dev != nullptr && r >= *n_rows_dev) return;
+  const long long src = row_index ? (long long)row_index[r] : (long long)r;
+  const uint8_t* row = x + src * x_pitch;
+  if (valid_off >= 0 && *reinterpret_cast<const int*>(row + valid_off) == 0) return;
+  const int chunks = hidden / 8;
+  const int groups = hidden / 128;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const uint4 v = reinterpret_cast<const uint4*>(row)[c];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float f[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+      amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+    }
+    // 16 consecutive threads hold one 128-wide group (chunks is a multiple of 16, so a group is either
+    // fully active or fully idle in the last sweep)
+    const unsigned active = __activemask();
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(active, amax, off));
+    const float scale = fmaxf(amax, 1e-10f) / 448.f;
+    const float inv = 1.f / scale;
+    uint2 packed;
+    uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      pb[i] = (uint8_t)__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3);
+    reinterpret_cast<uint2*>(q + (long long)r * hidden)[c] = packed;
+    if ((c & 15) == 0) scales[(long long)r * groups + (c >> 4)] = scale;
+  }
+}
+
+typedef CUresult (*F8EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+template <bool kGateUp, int N_MAX>
+static int launch_f8(const void* tmap, const mf_gemm_args* args, int grid, cudaStream_t stream) {
+  using Cfg = F8Cfg<kGateUp, N_MAX>;
+  static bool configured = false;
+  auto kern = grouped_gemm_fp8_kernel<kGateUp, N_MAX>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap tm;
+  memcpy(&tm, tmap, sizeof(tm));
+  return (int)launch_kernel(kern, dim3(grid), dim3(kF8Threads), Cfg::kSmemBytes, stream, true, tm, *args);
+}
+
+static int check_f8(const mf_gemm_args* a, int n_max, int grid) {
+  if (!a || grid < 1) return -1;
+  if (n_max != 32 && n_max != 64) return -2;
+  if (a->m_blocks < 1 || a->k_blocks < 1 || a->k_blocks > kF8MaxKb) return -3;
+  if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
+  if (!a->w_scale || !a->b_scale) return -5;
+  return 0;
+}
+
+}  // namespace mf
+
+extern "C" {
+
+int mf_gemm_gate_up_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
+  int c = mf::check_f8(args, n_max, grid);
+  if (c) return c;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_max == 32) return mf::launch_f8<true, 32>(tmap, args, grid, s);
+  return mf::launch_f8<true, 64>(tmap, args, grid, s);
+}
+
+int mf_gemm_down_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
+  int c = mf::check_f8(args, n_max, grid);
+  if (c) return c;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_max == 32) return mf::launch_f8<false, 32>(tmap, args, grid, s);
+  return mf::launch_f8<false, 64>(tmap, args, grid, s);
+}
+
+int mf_quant_rows_1x128(const void* x, long long x_pitch, const int* row_index, int rows, int hidden, void* q,
+                        float* scales, long long valid_off, const int* n_rows_dev, mf_stream_t stream) {
+  if (rows == 0) return 0;
+  if (hidden % 128 != 0 || (x_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return -1;
+  return (int)mf::launch_kernel(mf::quant_rows_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), true,
+                                static_cast<const uint8_t*>(x), x_pitch, row_index, hidden, static_cast<uint8_t*>(q),
+                                scales, valid_off, n_rows_dev);
+}
+
+}  // extern "C"

@@ -182,8 +182,15 @@ typedef struct {
 int mf_combine(const mf_combine_args* args, mf_stream_t stream);
 
 // ---- activation quantisation (1x128 groups -> e4m3 + fp32 scales) --------------------------------------
+// q[r, :] = e4m3(x[src(r), :] / scale), scales[r, g] = max(amax_g, 1e-10) / 448 for every 128-wide group g.
+// src(r) = row_index ? row_index[r] : r.  With valid_off >= 0 a source row whose int32 at that byte offset is
+// zero is skipped; with n_rows_dev != NULL rows r >= *n_rows_dev are skipped.
 int mf_quant_rows_1x128(const void* x, long long x_pitch, const int* row_index, int rows, int hidden, void* q,
-                        float* scales, mf_stream_t stream);
+                        float* scales, long long valid_off, const int* n_rows_dev, mf_stream_t stream);
+// Block-scaled e4m3 variants of the grouped GEMMs (args->w_scale, b_scale, b_scale_pitch are required;
+// b_base rows are e4m3 bytes, k_blocks = K / 128, the tensor map is built with elem_bytes = 1; n_max 32 or 64).
+int mf_gemm_gate_up_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);
+int mf_gemm_down_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);
 
 // ---- peer-memory runtime ------------------------------------------------------------------------------------
 int mf_peer_alloc(void** ptr, unsigned long long bytes);
