@@ -507,10 +507,10 @@ class FixedEPLayer:
             ring=int(self.combine_mode == "bf16_ring"), status=self.status.data_ptr(), wait_ns=self.wait_ns,
         )
         self._tmap13 = self._tmap2 = None
+        self._fp8 = None  # set by set_weights_fp8
+        self._lib = _lib.lib()
         if self.w13 is not None:
             self.set_weights(self.w13, self.w2)
-        self._lib = _lib.lib()
-        self._make_tmap = make_weight_tmap
 
     def set_weights(self, w13_local: torch.Tensor, w2_local: torch.Tensor) -> None:
         """(Re)bind the local expert shard: ``w13 [L, 2I, H]``, ``w2 [L, H, I]`` bf16, contiguous."""
@@ -522,8 +522,55 @@ class FixedEPLayer:
         if w13_local.dtype != torch.bfloat16 or w2_local.dtype != torch.bfloat16:
             raise ValueError("cuda backend takes bf16 weights")
         self.w13, self.w2 = w13_local.contiguous(), w2_local.contiguous()
+        self._fp8 = None
         self._tmap13 = make_weight_tmap(self.w13)
         self._tmap2 = make_weight_tmap(self.w2)
+
+    def set_weights_fp8(self, w13_q, w13_s, w2_q, w2_s) -> None:
+        """Bind block-scaled e4m3 expert weights (kept un-dequantised).
+
+        ``w13_q [L, 2I, H]`` / ``w2_q [L, H, I]`` float8_e4m3fn with fp32 scales per 128x128 block
+        (``w13_s [L, 2I/128, H/128]``, ``w2_s [L, H/128, I/128]``).  The forward then quantises the
+        received rows and the SwiGLU activations per 1x128 group on the device and runs the
+        ``kind::f8f6f4`` grouped GEMMs; inputs and outputs of the layer stay bf16.
+        """
+        from .ops import _lib
+        from .ops.kernels import make_weight_tmap
+
+        if self.backend != "cuda":
+            raise ValueError("fp8 weights need the cuda backend")
+        L, H, I, N = self.L, self.H, self.I, self.n_entries
+        if tuple(w13_q.shape) != (L, 2 * I, H) or tuple(w2_q.shape) != (L, H, I):
+            raise ValueError("weight shard has the wrong shape")
+        if w13_q.dtype != torch.float8_e4m3fn or w2_q.dtype != torch.float8_e4m3fn:
+            raise ValueError("e4m3 weights expected")
+        if tuple(w13_s.shape) != (L, 2 * I // 128, H // 128) or tuple(w2_s.shape) != (L, H // 128, I // 128):
+            raise ValueError("scales must be one fp32 per 128x128 block")
+        if H > 4096 or I > 4096 or self.block_m > 64:
+            raise ValueError("fp8 path supports K <= 4096 and block_m <= 64")
+        dev = self.device
+        f = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
+             "s2": w2_s.to(torch.float32).contiguous()}
+        f["tm13"] = make_weight_tmap(f["w13"].view(torch.uint8))
+        f["tm2"] = make_weight_tmap(f["w2"].view(torch.uint8))
+        rows = self.world * self.C
+        f["xq"] = torch.zeros(rows, H, dtype=torch.uint8, device=dev)
+        f["xs"] = torch.zeros(rows, H // 128, dtype=torch.float32, device=dev)
+        f["aq"] = torch.zeros(N, I, dtype=torch.uint8, device=dev)
+        f["as"] = torch.zeros(N, I // 128, dtype=torch.float32, device=dev)
+        g1, g2 = self._a_gemm1, self._a_gemm2
+        common = dict(tile_e=g1.tile_e, tile_s=g1.tile_s, tile_n=g1.tile_n, plan=g1.plan, partial=g1.partial,
+                      max_split_slots=g1.max_split_slots, limit=g1.limit, round_h=0, status=g1.status, wait_ns=g1.wait_ns)
+        f["a1"] = _lib.GemmArgs(b_base=f["xq"].data_ptr(), b_pitch=H, b_index=self.entry_row.data_ptr(),
+                                split_word=_lib.PLAN_SPLIT1, m_blocks=I // 128, k_blocks=H // 128, rows_per_expert=2 * I,
+                                up_row_offset=I, out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=g1.counters,
+                                w_scale=f["s13"].data_ptr(), b_scale=f["xs"].data_ptr(), b_scale_pitch=H // 128, **common)
+        f["a2"] = _lib.GemmArgs(b_base=f["aq"].data_ptr(), b_pitch=I, b_index=None, split_word=_lib.PLAN_SPLIT2,
+                                m_blocks=H // 128, k_blocks=I // 128, rows_per_expert=H, up_row_offset=0,
+                                out=self.y.data_ptr(), out_pitch=H, row_scale=self.entry_w.data_ptr(), counters=g2.counters,
+                                w_scale=f["s2"].data_ptr(), b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128, **common)
+        self._fp8 = f
+        self._tmap13, self._tmap2 = f["tm13"], f["tm2"]
 
     def make_weight_maps(self, w13_local: torch.Tensor, w2_local: torch.Tensor):
         """TMA descriptors for a weight pair (build once per MoE layer, then pass to ``bind_weights``)."""
@@ -541,6 +588,7 @@ class FixedEPLayer:
         if tmap13 is None or tmap2 is None:
             self.set_weights(w13_local, w2_local)
             return
+        self._fp8 = None
         self.w13, self.w2, self._tmap13, self._tmap2 = w13_local, w2_local, tmap13, tmap2
 
     def _cuda_dispatch(self, x, weights, ids, num_valid, logits=None, bias=None) -> torch.Tensor:
@@ -583,6 +631,22 @@ class FixedEPLayer:
         s = _lib.stream_ptr()
         self._cuda_meta()
         if stop_after == "META":
+            return
+        if self._fp8 is not None:
+            f, lib = self._fp8, self._lib
+            valid_off = self.H * 2 + 2 * self.K * 4  # byte offset of a received row's valid flag
+            _lib.check(lib.mf_quant_rows_1x128(self._recv_store.data_ptr(), self.pitch * 2, None, self.world * self.C, self.H,
+                                               f["xq"].data_ptr(), f["xs"].data_ptr(), valid_off, None, s), "quantise rows")
+            _lib.check(lib.mf_gemm_gate_up_fp8(f["tm13"], C.byref(f["a1"]), self.block_m, self.n_sms, s), "fp8 gate/up gemm")
+            if stop_after == "GEMM1":
+                return
+            entries = self.plan[_lib.PLAN_N_ENTRIES :]
+            _lib.check(lib.mf_quant_rows_1x128(self.act.data_ptr(), self.I * 2, None, self.n_entries, self.I, f["aq"].data_ptr(),
+                                               f["as"].data_ptr(), -1, entries.data_ptr(), s), "quantise activations")
+            _lib.check(lib.mf_gemm_down_fp8(f["tm2"], C.byref(f["a2"]), self.block_m, self.n_sms, s), "fp8 down gemm")
+            if stop_after == "GEMM2":
+                return
+            _lib.check(lib.mf_owner_reduce_push(C.byref(self._a_reduce), s), "owner_reduce_push")
             return
         _lib.check(self._lib.mf_gemm_gate_up(self._tmap13, C.byref(self._a_gemm1), self.block_m, self.n_sms, s), "gate/up gemm")
         if stop_after == "GEMM1":
