@@ -47,6 +47,7 @@ def main() -> None:
     ap.add_argument("--small", action="store_true", help="small layer shape (smoke runs)")
     ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (keeps hidden/intermediate)")
     ap.add_argument("--only-full", action="store_true", help="time only the whole layer (profiling runs)")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights (quantised from the bf16 ones)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     info = init_dist()
@@ -57,6 +58,17 @@ def main() -> None:
         cfg = dataclasses.replace(cfg, n_routed_experts=args.experts)
     w13, w2 = _weights(cfg, info.rank, info.world, info.device)
     bias = make_bias(cfg, 1, device=info.device)
+    fp8_pack = None
+    if args.fp8:
+        from ..weights import quant_block_fp8
+
+        def pack(w):
+            qs, ss = zip(*(quant_block_fp8(w[e]) for e in range(w.shape[0])))
+            return torch.stack([q.view(torch.uint8) for q in qs]).view(torch.float8_e4m3fn), torch.stack(ss)
+
+        q13, s13 = pack(w13)
+        q2, s2 = pack(w2)
+        fp8_pack = (q13, s13, q2, s2)
     flush = None if args.no_flush else L2Flush(device=info.device)
     stages = list(STAGES)
     if args.only_full:
@@ -67,6 +79,8 @@ def main() -> None:
     points = []
     for T in [int(t) for t in args.tokens.split(",")]:
         layer = FixedEPLayer(cfg, info.rank, info.world, w13, w2, capacity=T, backend=args.backend)
+        if args.fp8:
+            layer.set_weights_fp8(*fp8_pack)
         x = make_hidden(T, cfg, 300 + T + info.rank, device=info.device)
         lg = make_logits(T, cfg, 400 + T + info.rank, dist=args.dist, device=info.device)
         prefix_us = {}

@@ -35,7 +35,7 @@ constexpr int kF8BlockM = 128;
 constexpr int kF8TileA = 128 * 128;
 constexpr int kF8Threads = 256;
 constexpr int kF8Gather = 64;
-constexpr int kF8TmpStages = 2;
+constexpr int kF8Tables = 3;  // scale tables: current unit, prefetched next unit, one in reserve
 constexpr int kF8MaxKb = 32;  // K <= 4096 (one unit never spans more K blocks than this)
 
 template <bool kGateUp, int N_MAX>
@@ -44,11 +44,15 @@ struct F8Cfg {
   static constexpr int kStageA = kATiles * kF8TileA;
   static constexpr int kStageB = N_MAX * 128;
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kTableBytes = 2 * (N_MAX * kF8MaxKb + 2 * kF8MaxKb) * 4;  // two unit parities
+  static constexpr int kTableFloats = N_MAX * kF8MaxKb + 2 * kF8MaxKb;
+  static constexpr int kTableBytes = kF8Tables * kTableFloats * 4;
   static constexpr int kStages = (200 * 1024 - kTableBytes) / kStageBytes > 8 ? 8 : (200 * 1024 - kTableBytes) / kStageBytes;
   static constexpr int kTmpCols = kATiles * N_MAX;
-  static constexpr int kTmemCols = kF8TmpStages * kTmpCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kTableBytes + 1024 + 256;
+  // One tensor-memory accumulator per K block in flight: the MMA -> promotion -> MMA round trip is about a
+  // microsecond, so two stages cannot keep up with the weight stream; use all 512 columns (at most 8 stages).
+  static constexpr int kTmpStages = 512 / kTmpCols > 8 ? 8 : 512 / kTmpCols;
+  static constexpr int kTmemCols = kTmpStages * kTmpCols;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kTableBytes + 1024 + 512;
 };
 
 struct F8Pipe {
@@ -72,14 +76,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * Cfg::kStageA;
-  float* sTable = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);  // [2][N_MAX*kMaxKb + 2*kMaxKb]
+  float* sTable = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);  // [kF8Tables][kTableFloats]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes + Cfg::kTableBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tmp_full = bars + 2 * STAGES;
-  uint64_t* tmp_empty = tmp_full + kF8TmpStages;
-  uint64_t* tbl_bar = tmp_empty + kF8TmpStages;  // [2] one per unit parity
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_bar + 2);
+  uint64_t* tmp_empty = tmp_full + Cfg::kTmpStages;
+  uint64_t* tbl_bar = tmp_empty + Cfg::kTmpStages;  // [kF8Tables]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_bar + kF8Tables);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -88,12 +92,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
       mbar_init(&full_bar[s], 1 + kF8Gather);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int s = 0; s < kF8TmpStages; ++s) {
+    for (int s = 0; s < Cfg::kTmpStages; ++s) {
       mbar_init(&tmp_full[s], 1);
       mbar_init(&tmp_empty[s], 4);
     }
-    mbar_init(&tbl_bar[0], 4);
-    mbar_init(&tbl_bar[1], 4);
+    for (int s = 0; s < kF8Tables; ++s) mbar_init(&tbl_bar[s], 4);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
@@ -183,7 +186,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
         }
         __syncwarp();
         st.advance(STAGES);
-        tmp.advance(kF8TmpStages);
+        tmp.advance(Cfg::kTmpStages);
       }
     }
   } else if (warp < 4) {
@@ -233,42 +236,49 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
     const int wq = warp & 3, row = wq * 32 + lane;
     F8Pipe tmp;
     bool ok = true;
-    uint32_t unit_parity = 0;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, unit_parity ^= 1u) {
-      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt], e = a.tile_e[tt];
-      int n_tile = (n_rows + 15) & ~15;
-      if (n_tile < 16) n_tile = 16;
-      const int kb0 = ks * kb_per;
-
-      // scale table of this unit: x scales [n][j] and weight scales [t][j], j = kb - kb0
-      float* tbl = sTable + unit_parity * (N_MAX * kF8MaxKb + 2 * kF8MaxKb);
-      float* tblW = tbl + N_MAX * kF8MaxKb;
-      const int row_blocks = a.rows_per_expert / kF8BlockM;
-      for (int n = wq; n < n_tile; n += 4) {
-        float v = 0.f;
-        const bool live = n < n_rows;
+    const int row_blocks = a.rows_per_expert / kF8BlockM;
+    // Scale table of unit `uu` into buffer `buf`: x scales [n][j] and weight scales [t][j], j = kb - kb0.
+    // Every epilogue warp fills a quarter and arrives once on the buffer's barrier.
+    auto load_table = [&](int uu, int buf) {
+      const int ks_ = uu % split, mb_ = (uu / split) % a.m_blocks, tt_ = uu / (split * a.m_blocks);
+      const int n_rows_ = a.tile_n[tt_], row_start_ = a.tile_s[tt_], e_ = a.tile_e[tt_];
+      int n_tile_ = (n_rows_ + 15) & ~15;
+      if (n_tile_ < 16) n_tile_ = 16;
+      const int kb0_ = ks_ * kb_per;
+      float* t = sTable + buf * Cfg::kTableFloats;
+      for (int n = wq; n < n_tile_; n += 4) {
+        const bool live = n < n_rows_;
         long long idx = 0;
-        if (live) idx = a.b_index ? (long long)a.b_index[row_start + n] : (long long)(row_start + n);
-        for (int j = lane; j < kb_per; j += 32) {
-          v = live ? a.b_scale[idx * a.b_scale_pitch + kb0 + j] : 0.f;
-          tbl[n * kF8MaxKb + j] = v;
-        }
+        if (live) idx = a.b_index ? (long long)a.b_index[row_start_ + n] : (long long)(row_start_ + n);
+        for (int j = lane; j < kb_per; j += 32) t[n * kF8MaxKb + j] = live ? a.b_scale[idx * a.b_scale_pitch + kb0_ + j] : 0.f;
       }
       if (wq < (kGateUp ? 2 : 1)) {
-        const int rb = (wq == 0 ? 0 : a.up_row_offset / kF8BlockM) + mb;
-        const float* ws = a.w_scale + ((long long)e * row_blocks + rb) * a.k_blocks + kb0;
-        for (int j = lane; j < kb_per; j += 32) tblW[wq * kF8MaxKb + j] = ws[j];
+        const int rb = (wq == 0 ? 0 : a.up_row_offset / kF8BlockM) + mb_;
+        const float* ws = a.w_scale + ((long long)e_ * row_blocks + rb) * a.k_blocks + kb0_;
+        for (int j = lane; j < kb_per; j += 32) t[N_MAX * kF8MaxKb + wq * kF8MaxKb + j] = ws[j];
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tbl_bar[unit_parity]);
-      // every second unit reuses a barrier: its phase is (number of earlier units with this parity) & 1
-      const uint32_t tbl_phase = (uint32_t)(((u - blockIdx.x) / gridDim.x) >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_bar[unit_parity], tbl_phase, abort_flag, wait_ns));
+      if (lane == 0) mbar_arrive(&tbl_bar[buf]);
+    };
+    if ((int)blockIdx.x < total_units) load_table(blockIdx.x, 0);
+    int it = 0;  // index of this CTA's unit
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
+      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
+      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt];
+      int n_tile = (n_rows + 15) & ~15;
+      if (n_tile < 16) n_tile = 16;
+      const int buf = it % kF8Tables;
+      const float* tbl = sTable + buf * Cfg::kTableFloats;
+      const float* tblW = tbl + N_MAX * kF8MaxKb;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_bar[buf], (uint32_t)(it / kF8Tables) & 1u, abort_flag, wait_ns));
       if (!ok) {
         if (lane == 0) report_status(a.status, kGemmAccTimeout, 4, blockIdx.x, 0);
         break;
       }
+      // Prefetch the next unit's table.  Its buffer was last read two units ago; having passed the wait
+      // above means all four warps filled table `it`, which they do inside unit `it - 1`, so no warp is
+      // still in unit `it - 2`.
+      if (u + (int)gridDim.x < total_units) load_table(u + gridDim.x, (it + 1) % kF8Tables);
 
       float acc_g[N_MAX], acc_u[kGateUp ? N_MAX : 1];
 #pragma unroll
@@ -306,7 +316,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmp_empty[tmp.stage]);
-        tmp.advance(kF8TmpStages);
+        tmp.advance(Cfg::kTmpStages);
       }
       if (!ok) break;
 
