@@ -342,13 +342,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
         }
       } else {
         const int tile_mb = tt * a.m_blocks + mb;
-        const long long slot_floats = (long long)Cfg::kATiles * N_MAX * kF8BlockM;
+        int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
+        if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
+        const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kF8BlockM;
         float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
 #pragma unroll
         for (int n = 0; n < N_MAX; ++n) {
           if (n < n_rows) {
             __stcg(&mine[(long long)n * kF8BlockM + row], acc_g[n]);
-            if (kGateUp) __stcg(&mine[(long long)(N_MAX + n) * kF8BlockM + row], acc_u[n]);
+            if (kGateUp) __stcg(&mine[(long long)(slot_cols + n) * kF8BlockM + row], acc_u[n]);
           }
         }
         __threadfence();
@@ -364,7 +366,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
             for (int s = 0; s < split; ++s) {
               const float* p = base + s * slot_floats;
               v += __ldcg(&p[(long long)n * kF8BlockM + row]);
-              if (kGateUp) w += __ldcg(&p[(long long)(N_MAX + n) * kF8BlockM + row]);
+              if (kGateUp) w += __ldcg(&p[(long long)(slot_cols + n) * kF8BlockM + row]);
             }
             if (kGateUp) {
               if (a.round_h) {

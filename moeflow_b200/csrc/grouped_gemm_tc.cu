@@ -83,6 +83,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  // Optional per-CTA time stamps: 0 entry, 1 dependencies met, 2 first weight tile requested, 3 first
+  // operand stage complete, 4 first accumulator complete, 5 last epilogue done, 6 exit.
+  unsigned long long* trace = a.trace ? a.trace + (size_t)blockIdx.x * 8 : nullptr;
+  if (trace && tid == 0) trace[0] = global_timer_ns();
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -118,6 +122,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
     if (warp >= 2) grid_dep_wait();  // token-operand producers (act rows) and epilogue (arrival counters)
   }
 
+  if (trace && tid == 0) trace[1] = global_timer_ns();
   const int n_tiles = a.plan[MF_PLAN_N_TILES];
   int split = a.plan[a.split_word];
   if (split < 1) split = 1;
@@ -146,6 +151,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageA);
           uint8_t* dst = sA + st.stage * Cfg::kStageA;
+          if (trace && trace[2] == 0) trace[2] = global_timer_ns();
           tma_load_2d(dst, &tmap_w, &full_bar[st.stage], kb * 64, row0);
           if (kGateUp) tma_load_2d(dst + kTileBytesA, &tmap_w, &full_bar[st.stage], kb * 64, row0 + a.up_row_offset);
         }
@@ -178,6 +184,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
       for (int j = 0; j < kb_per; ++j) {
         ok = mbar_wait_bounded(&full_bar[st.stage], st.phase, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
+        if (trace && lane == 0 && trace[3] == 0) trace[3] = global_timer_ns();
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmFullTimeout, 1, blockIdx.x, 0);
           break;
@@ -269,6 +276,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
       if (n_tile < 16) n_tile = 16;
       ok = mbar_wait_bounded(&acc_full[acc.stage], acc.phase, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
+      if (trace && warp == 4 && lane == 0 && trace[4] == 0) trace[4] = global_timer_ns();
       if (!ok) {
         if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
         break;
@@ -309,7 +317,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
       } else {
         // Split K: park the fp32 partial sums, then the last quarter-warp to arrive reduces them.
         const int tile_mb = tt * a.m_blocks + mb;
-        const long long slot_floats = (long long)Cfg::kATiles * N_MAX * kBlockM;
+        int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
+        if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
+        const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kBlockM;
         float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           uint32_t g[16], up[16];
@@ -321,7 +331,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
             const int n = c0 + j;
             if (n < n_rows) {
               __stcg(&mine[(long long)n * kBlockM + row], __uint_as_float(g[j]));
-              if (kGateUp) __stcg(&mine[(long long)(N_MAX + n) * kBlockM + row], __uint_as_float(up[j]));
+              if (kGateUp) __stcg(&mine[(long long)(slot_cols + n) * kBlockM + row], __uint_as_float(up[j]));
             }
           }
         }
@@ -341,7 +351,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
             for (int s = 0; s < split; ++s) {
               const float* p = base + s * slot_floats;
               v += __ldcg(&p[(long long)n * kBlockM + row]);
-              if (kGateUp) w += __ldcg(&p[(long long)(N_MAX + n) * kBlockM + row]);
+              if (kGateUp) w += __ldcg(&p[(long long)(slot_cols + n) * kBlockM + row]);
             }
             if (kGateUp) {
               if (a.round_h) {
@@ -358,12 +368,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
         }
       }
       acc.advance(kAccStages);
+      if (trace && warp == 4 && lane == 0) trace[5] = global_timer_ns();
     }
   }
 
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
+  if (trace && tid == 0) trace[6] = global_timer_ns();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);

@@ -17,6 +17,7 @@ enum {
   MF_PLAN_SPLIT1 = 1,     // K split of the gate/up GEMM
   MF_PLAN_SPLIT2 = 2,     // K split of the down GEMM
   MF_PLAN_N_ENTRIES = 3,  // valid (row, slot) entries = offsets[L]
+  MF_PLAN_SLOT_COLS = 4,  // token columns per split-K partial slot (multiple of 16; 0 = the kernel's n_max)
   MF_PLAN_WORDS = 8
 };
 
@@ -48,7 +49,8 @@ typedef struct {
   const float* w_scale;      // [experts, rows_per_expert/128, K/128] fp32 (weight_scale_inv)
   const float* b_scale;      // [b rows, K/128] fp32 activation scales (1x128 groups)
   long long b_scale_pitch;   // floats between rows of b_scale
-  float* out_scale;          // gate/up fp8 output: [entries, I/128] scales of the quantised activation
+  float* out_scale;          // reserved
+  unsigned long long* trace; // optional [grid, 8] globaltimer stamps per CTA (profiling aid), or NULL
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
@@ -147,9 +149,10 @@ typedef struct {
   int max_tiles;
   int m_blocks1, k_blocks1, m_blocks2, k_blocks2;
   int n_sms;
-  int max_split_slots;
+  int max_split_slots;       // unused when partial_floats > 0
   unsigned long long* status;
   unsigned long long wait_ns;
+  long long partial_floats;  // capacity of the split-K scratch in floats: bounds slots = floats / (tiles * cols * 128)
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 

@@ -447,7 +447,10 @@ class FixedEPLayer:
         mb1, mb2 = I // 128, H // 128
         self._counters1 = torch.zeros(self.max_tiles * mb1 * 4, **i32)
         self._counters2 = torch.zeros(self.max_tiles * mb2 * 4, **i32)
-        self._partial = torch.zeros(self.max_split_slots * 2 * self.block_m * 128, dtype=torch.float32, device=dev)
+        # split-K scratch: a byte budget; the metadata kernel sizes the partial slots for the widest token tile
+        partial_floats = int(self.gemm_kwargs.get("split_scratch_mb", 64)) * (1 << 20) // 4
+        self.max_split_slots = partial_floats // (2 * self.block_m * 128)
+        self._partial = torch.zeros(partial_floats, dtype=torch.float32, device=dev)
         self._keep: list = []  # ctypes objects and temporaries that must outlive launches
 
         S = _lib
@@ -471,6 +474,7 @@ class FixedEPLayer:
             n_counters2=self._counters2.numel(), block_m=self.block_m, max_tiles=self.max_tiles, m_blocks1=mb1,
             k_blocks1=H // 64, m_blocks2=mb2, k_blocks2=I // 64, n_sms=self.n_sms,
             max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
+            partial_floats=partial_floats,
         )
         limit = cfg.swiglu_limit if cfg.swiglu_limit is not None else 0.0
         common = dict(

@@ -13,7 +13,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libmoeflow_b200.so"
 
-PLAN_N_TILES, PLAN_SPLIT1, PLAN_SPLIT2, PLAN_N_ENTRIES, PLAN_WORDS = 0, 1, 2, 3, 8
+PLAN_N_TILES, PLAN_SPLIT1, PLAN_SPLIT2, PLAN_N_ENTRIES, PLAN_SLOT_COLS, PLAN_WORDS = 0, 1, 2, 3, 4, 8
 
 STATUS_NAMES = {
     0: "ok",
@@ -56,6 +56,7 @@ class GemmArgs(C.Structure):
         ("b_scale", C.c_void_p),
         ("b_scale_pitch", C.c_longlong),
         ("out_scale", C.c_void_p),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -126,6 +127,7 @@ class MetaArgs(C.Structure):
         ("max_split_slots", C.c_int),
         ("status", C.c_void_p),
         ("wait_ns", C.c_ulonglong),
+        ("partial_floats", C.c_longlong),
     ]
 
 
