@@ -21,11 +21,12 @@ namespace mf {
 
 constexpr int kDispatchThreads = 256;
 constexpr int kMaxTopK = 32;
+constexpr int kMaxRanks = 256;
 
 __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const mf_dispatch_args a) {
   __shared__ int s_id[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
-  __shared__ int s_present;
+  __shared__ unsigned char s_present[kMaxRanks];
 
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
@@ -72,16 +73,19 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
   }
   __syncthreads();
 
+  // Which destinations does this token hit?  One thread per destination, once; the copy loop below then
+  // needs no barrier, so the stores to all peers are in flight together.
+  for (int d = tid; d < a.R; d += kDispatchThreads) {
+    int present = 0;
+    if (live)
+      for (int k = 0; k < a.K; ++k) present |= (s_id[k] >= 0 && s_id[k] / a.L == d) ? 1 : 0;
+    s_present[d] = (unsigned char)present;
+    a.hit[(size_t)t * a.R + d] = (unsigned char)present;
+  }
+  __syncthreads();
+
   for (int d = 0; d < a.R; ++d) {
-    if (tid == 0) {
-      int present = 0;
-      if (live)
-        for (int k = 0; k < a.K; ++k) present |= (s_id[k] >= 0 && s_id[k] / a.L == d) ? 1 : 0;
-      s_present = present;
-      a.hit[(size_t)t * a.R + d] = (unsigned char)present;
-    }
-    __syncthreads();
-    const int present = s_present;
+    const int present = s_present[d];
     uint8_t* row = reinterpret_cast<uint8_t*>(a.peer_recv[d]) + ((size_t)a.rank * a.C + t) * a.pitch;
     if (has_token && (present || !a.skip_payload)) {
       uint4* dst = reinterpret_cast<uint4*>(row);
@@ -99,7 +103,6 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
     } else if (tid == a.K) {
       meta[2 * a.K] = present;
     }
-    __syncthreads();
   }
 
   // Publish: every thread's stores are fenced at system scope, then the CTA counts itself done.
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
 }  // namespace mf
 
 extern "C" int mf_dispatch_push(const mf_dispatch_args* a, mf_stream_t stream) {
-  if (!a || a->C < 1 || a->T > a->C || a->K > mf::kMaxTopK || a->H % 8 != 0 ||
+  if (!a || a->C < 1 || a->T > a->C || a->K > mf::kMaxTopK || a->R > mf::kMaxRanks || a->H % 8 != 0 ||
       a->H / 8 > mf::kDispatchThreads * 4 || (a->pitch & 15) != 0 || a->pitch < (long long)a->H * 2 + (2 * a->K + 1) * 4)
     return -1;
   size_t smem = 0;
