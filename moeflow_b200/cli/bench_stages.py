@@ -78,7 +78,8 @@ def main() -> None:
         stages = stages[:at] + list(CUDA_SUBSTAGES) + stages[at:]
     points = []
     for T in [int(t) for t in args.tokens.split(",")]:
-        layer = FixedEPLayer(cfg, info.rank, info.world, w13, w2, capacity=T, backend=args.backend)
+        layer = FixedEPLayer(cfg, info.rank, info.world, w13, w2, capacity=T, backend=args.backend,
+                             gemm_kwargs={"block_m": 64} if args.fp8 else None)
         if args.fp8:
             layer.set_weights_fp8(*fp8_pack)
         x = make_hidden(T, cfg, 300 + T + info.rank, device=info.device)

@@ -420,7 +420,10 @@ class FixedEPLayer:
 
         i32 = dict(dtype=torch.int32, device=dev)
         N = self.n_entries
-        self.block_m = int(self.gemm_kwargs.get("block_m", 64))
+        # token rows per tile: 64 for decode; 128 when experts see many rows (prefill), which halves the
+        # number of times an expert's weights are streamed
+        rows_per_expert = (R * Cc * K) / max(L, 1)
+        self.block_m = int(self.gemm_kwargs.get("block_m", 128 if rows_per_expert >= 96 else 64))
         if self.block_m not in (32, 64, 128):
             raise ValueError("block_m must be 32, 64 or 128")
         self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
@@ -551,7 +554,7 @@ class FixedEPLayer:
         if tuple(w13_s.shape) != (L, 2 * I // 128, H // 128) or tuple(w2_s.shape) != (L, H // 128, I // 128):
             raise ValueError("scales must be one fp32 per 128x128 block")
         if H > 4096 or I > 4096 or self.block_m > 64:
-            raise ValueError("fp8 path supports K <= 4096 and block_m <= 64")
+            raise ValueError("fp8 path supports K <= 4096 and block_m <= 64 (build the layer with gemm_kwargs={'block_m': 64})")
         dev = self.device
         f = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
              "s2": w2_s.to(torch.float32).contiguous()}
