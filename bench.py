@@ -150,13 +150,22 @@ def make_local_weights(rank: int, world: int, dev: torch.device):
     return w13, w2
 
 
+ROUTING = "uniform"  # set from --dist
+
+
 def make_inputs(tokens: int, rank: int, pool: int, pinned: bool):
-    """``pool`` input sets of hidden states ``[T, H]`` bf16 and uniform router logits ``[T, E]`` fp32 (host)."""
+    """``pool`` input sets of hidden states ``[T, H]`` bf16 and router logits ``[T, E]`` fp32 (host).
+
+    ``uniform``: i.i.d. normal logits.  ``zipf``: expert e gets the offset ``-2 * 1.2 * log(e + 1)``, so
+    popularity follows Zipf(1.2) in expert-id order and the hot experts sit together on rank 0.
+    """
     xs, lgs = [], []
     for i in range(pool):
         g = torch.Generator().manual_seed(7919 * tokens + 104729 * rank + i)
         x = torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16)
         lg = torch.randn(tokens, EXPERTS, generator=g)
+        if ROUTING == "zipf":
+            lg = lg - 2.0 * 1.2 * torch.log(torch.arange(1, EXPERTS + 1, dtype=torch.float32))
         if pinned:
             x, lg = x.pin_memory(), lg.pin_memory()
         xs.append(x)
@@ -321,9 +330,12 @@ def main() -> None:
     ap.add_argument("--impl", default="moeflow_b200", choices=["moeflow_b200", "reference"])
     ap.add_argument("--tokens", type=int, default=128, help="headline tokens per rank")
     ap.add_argument("--no-sweep", action="store_true", help="skip the T = 1..128 sweep")
+    ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"], help="routing popularity profile")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    global ROUTING
+    ROUTING = args.dist
 
     if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "moeflow" / "fixed.py").exists():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of /root/reference)"}))
@@ -389,7 +401,7 @@ def main() -> None:
                 "tokens_per_rank": args.tokens,
                 "seq_len": 1,
                 "parallelism": f"ep{world}",
-                "routing": "uniform",
+                "routing": args.dist,
                 "l2": "256 MiB buffer written before every timed step (L2 flush); local expert weights >> L2",
                 "timing": "per-step CUDA events, barrier-aligned, sum over steps, max over ranks",
                 "published_baseline_note": "published number is EP=4, intermediate 2048, real weights, L2-warm replays",

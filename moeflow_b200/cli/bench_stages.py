@@ -47,6 +47,7 @@ def main() -> None:
     ap.add_argument("--small", action="store_true", help="small layer shape (smoke runs)")
     ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (keeps hidden/intermediate)")
     ap.add_argument("--only-full", action="store_true", help="time only the whole layer (profiling runs)")
+    ap.add_argument("--fuse-return", type=int, default=None, help="1/0: owner reduce + return push inside the down GEMM or as its own kernel")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights (quantised from the bf16 ones)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
@@ -79,7 +80,8 @@ def main() -> None:
     points = []
     for T in [int(t) for t in args.tokens.split(",")]:
         layer = FixedEPLayer(cfg, info.rank, info.world, w13, w2, capacity=T, backend=args.backend,
-                             gemm_kwargs={"block_m": 64} if args.fp8 else None)
+                             gemm_kwargs={**({"block_m": 64} if args.fp8 else {}),
+                                          **({"fuse_return": bool(args.fuse_return)} if args.fuse_return is not None else {})})
         if args.fp8:
             layer.set_weights_fp8(*fp8_pack)
         x = make_hidden(T, cfg, 300 + T + info.rank, device=info.device)

@@ -148,6 +148,22 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
       }
     }
   }
+  // per received row: number of slots that live here (the fused return path of the down GEMM needs it),
+  // and the number of rows with at least one
+  if (tid == 0) warp_sums[35] = 0;
+  __syncthreads();
+  if (a.row_hits != nullptr) {
+    int mine = 0;
+    for (int r = tid; r < a.rows; r += kMetaThreads) {
+      const int* meta = reinterpret_cast<const int*>(recv + (size_t)r * a.pitch + meta_off);
+      int hits = 0;
+      if (meta[2 * K] != 0)
+        for (int k = 0; k < K; ++k) hits += (meta[k] >= 0 && meta[k] < L) ? 1 : 0;
+      a.row_hits[r] = hits;
+      mine += hits > 0 ? 1 : 0;
+    }
+    if (mine) atomicAdd(&warp_sums[35], mine);
+  }
   // widest token tile: the split-K partial slots are sized for it, so a decode step (few rows per
   // expert) can afford many more, smaller K splits than the worst case would allow
   if (tid == 0) warp_sums[34] = 0;
@@ -171,6 +187,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
     a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8);
     a.plan[MF_PLAN_N_ENTRIES] = n_entries;
     a.plan[MF_PLAN_SLOT_COLS] = cols;
+    a.plan[MF_PLAN_VALID_ROWS] = warp_sums[35];
   }
   __syncthreads();
 

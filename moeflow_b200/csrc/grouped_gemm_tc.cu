@@ -35,6 +35,8 @@ namespace mf {
 constexpr int kBlockM = 128;          // weight rows per block (UMMA M)
 constexpr int kTileBytesA = 128 * 128;  // 128 rows x 128 bytes
 constexpr int kThreads = 256;
+constexpr int kThreadsWithReturn = 384;  // + 4 return warps (fused owner reduce + return push)
+constexpr int kRetDepth = 4;            // queued unit descriptors per quarter
 constexpr int kGatherThreads = 64;
 constexpr int kAccStages = 2;
 
@@ -48,7 +50,7 @@ struct GemmCfg {
   static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
   static constexpr int kAccCols = kATiles * N_MAX;
   static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128}
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/;
 };
 
 struct PipeState {
@@ -62,8 +64,91 @@ struct PipeState {
   }
 };
 
-template <bool kGateUp, int N_MAX>
-__global__ void __launch_bounds__(kThreads, 1)
+// Fused owner reduce + return push, called by one epilogue warp after it has written the final y values
+// of `n_rows` entries (first entry `row_start`) for its 32 columns `col0 .. col0+31` of block `mb`.
+// For every entry the warp counts one arrival on (received row, block, quarter); the arrival that
+// completes a row's hit count sums that row's slots in slot order (fp32, +0.0 start), rounds once to
+// bf16 and stores the 32 values into the source rank's combine buffer.  Completed quarters are counted
+// on `ret_done`; the warp that brings it to valid_rows * m_blocks * 4 publishes the return flags.
+// Returns the number of (row, block, quarter) reductions this call completed; the caller adds them up and
+// reports them once with return_finish (one system-scope fence per warp, not per unit).
+__device__ __forceinline__ int return_rows(const mf_gemm_args& a, int n_rows, int row_start, int mb, int wq, int lane) {
+  const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(a.out);
+  const long long col0 = (long long)mb * kBlockM + wq * 32;  // this quarter's 32 columns (64 bytes, 64-byte aligned)
+  int completed = 0;
+  for (int n0 = 0; n0 < n_rows; n0 += 32) {
+    // One lane per entry: count the arrival; the lane whose arrival completes the row does the whole row
+    // (all its slots, 32 columns) by itself, so the rows of a unit are reduced in parallel, not in turn.
+    const int n = n0 + lane;
+    int r = -1;
+    bool last = false;
+    if (n < n_rows) {
+      r = a.entry_row[row_start + n];
+      int* cnt = a.row_cnt + ((long long)r * a.m_blocks + mb) * 4 + wq;
+      const int old = atomicAdd(cnt, 1);
+      last = (old + 1 == a.row_hits[r]);
+      if (last) *cnt = 0;  // self-cleaning: nobody else touches this counter again in this forward
+    }
+    const unsigned todo = __ballot_sync(0xffffffffu, last);
+    if (todo == 0u) continue;
+    __threadfence();  // the other slots' y values (written by other CTAs) are visible now
+    if (last) {
+      float acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+      for (int k = 0; k < a.ret_K; ++k) {
+        const int p = a.inv[(long long)r * a.ret_K + k];
+        if (p < 0) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(y + (long long)p * a.out_pitch + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 v = __ldcg(src + q);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            acc[q * 8 + 2 * i] += f.x;
+            acc[q * 8 + 2 * i + 1] += f.y;
+          }
+        }
+      }
+      const int src_rank = r / a.ret_C, t = r - src_rank * a.ret_C;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.ret_peer[src_rank]) +
+                                            ((long long)a.ret_rank * a.ret_C + t) * a.out_pitch + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[q * 8 + 2 * i], acc[q * 8 + 2 * i + 1]);
+        dst[q] = o;
+      }
+    }
+    completed += __popc(todo);
+  }
+  return completed;
+}
+
+// Report `completed` reductions of this warp; the warp that brings the layer's counter to
+// valid_rows * m_blocks * 4 publishes the return flags to every source rank.
+__device__ __forceinline__ void return_finish(const mf_gemm_args& a, int completed, int lane) {
+  if (completed == 0) return;
+  __threadfence_system();  // the peer stores of all lanes precede the count (and so the flags)
+  __syncwarp();
+  if (lane == 0) {
+    const unsigned total = (unsigned)a.plan[MF_PLAN_VALID_ROWS] * (unsigned)a.m_blocks * 4u;
+    const unsigned before = atomicAdd(a.ret_done, (unsigned)completed);
+    if (before + (unsigned)completed == total) {
+      __threadfence_system();
+      *a.ret_done = 0u;
+      const unsigned epoch = *a.ret_epoch;
+      for (int d = 0; d < a.ret_R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.ret_flag[d]) + a.ret_rank, epoch);
+    }
+  }
+}
+
+template <bool kGateUp, int N_MAX, bool kReturn = false>
+__global__ void __launch_bounds__(kReturn ? kThreadsWithReturn : kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_args a) {
   using Cfg = GemmCfg<kGateUp, N_MAX>;
   constexpr int STAGES = Cfg::kStages;
@@ -77,8 +162,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
   uint64_t* empty_bar = bars + STAGES;                // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;             // [kAccStages]
   uint64_t* acc_empty = acc_full + kAccStages;        // [kAccStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
+  uint64_t* ret_full = acc_empty + kAccStages;        // [4][kRetDepth] epilogue warp -> return warp
+  uint64_t* ret_empty = ret_full + 4 * kRetDepth;     // [4][kRetDepth]
+  int* ret_desc = reinterpret_cast<int*>(ret_empty + 4 * kRetDepth);  // [4][kRetDepth][4]: n_rows, row_start, mb
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ret_desc + 4 * kRetDepth * 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // The fused return path runs on four extra warps (the kernel is then launched with 384 threads).
+  constexpr bool with_return = kReturn;  // the down GEMM with four extra warps for the fused return path
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -96,6 +186,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&acc_full[s], 1);   // tcgen05.commit
       mbar_init(&acc_empty[s], 4);  // one per epilogue warp
+    }
+    for (int s = 0; s < 4 * kRetDepth; ++s) {
+      mbar_init(&ret_full[s], 1);
+      mbar_init(&ret_empty[s], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -123,6 +217,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
   }
 
   if (trace && tid == 0) trace[1] = global_timer_ns();
+  if (kReturn && blockIdx.x == 0 && tid == 64) {
+    // Fused return path with nothing to return: the flags must still be published (thread 64 belongs to
+    // the warps that waited for the previous kernel).
+    if (a.plan[MF_PLAN_VALID_ROWS] == 0) {
+      const unsigned epoch = *a.ret_epoch;
+      for (int d = 0; d < a.ret_R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.ret_flag[d]) + a.ret_rank, epoch);
+    }
+  }
   const int n_tiles = a.plan[MF_PLAN_N_TILES];
   int split = a.plan[a.split_word];
   if (split < 1) split = 1;
@@ -260,12 +362,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
     }
     // Drain this thread's cp.async operations before the CTA may exit.
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ epilogue
     const int wq = warp & 3;                 // TMEM lane quarter this warp may read
     const int row = wq * 32 + lane;          // weight row inside the block
     PipeState acc;
+    PipeState rq;                            // position in this quarter's return queue
     bool ok = true;
+    // Hand a finished unit (final y values stored) to this quarter's return warp.  n_rows < 0 ends it.
+    auto enqueue_return = [&](int n_rows_, int row_start_, int mb_) -> bool {
+      __threadfence();  // the y stores of all lanes are visible device-wide before the hand-over
+      __syncwarp();
+      const int slot = wq * kRetDepth + rq.stage;
+      bool k = mbar_wait_bounded(&ret_empty[slot], rq.phase ^ 1u, abort_flag, wait_ns);
+      k = __all_sync(0xffffffffu, k);
+      if (!k) return false;
+      if (lane == 0) {
+        int* d = ret_desc + slot * 4;
+        d[0] = n_rows_;
+        d[1] = row_start_;
+        d[2] = mb_;
+        mbar_arrive(&ret_full[slot]);
+      }
+      __syncwarp();
+      rq.advance(kRetDepth);
+      return true;
+    };
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
       const int ks = u % split;
       const int mb = (u / split) % a.m_blocks;
@@ -314,6 +436,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
+        if (with_return) ok = enqueue_return(n_rows, row_start, mb);
       } else {
         // Split K: park the fp32 partial sums, then the last quarter-warp to arrive reduces them.
         const int tile_mb = tt * a.m_blocks + mb;
@@ -365,11 +488,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
             out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
           }
           if (lane == 0) a.counters[tile_mb * 4 + wq] = 0;
+          if (with_return) ok = enqueue_return(n_rows, row_start, mb);
         }
       }
       acc.advance(kAccStages);
       if (trace && warp == 4 && lane == 0) trace[5] = global_timer_ns();
     }
+    if (with_return) enqueue_return(-1, 0, 0);  // tell the return warp that nothing more will come
+  } else {
+    // ------------------------------------------------------------------ return warps (fused owner reduce + push)
+    const int wq = warp & 3;
+    PipeState rq;
+    int completed = 0;
+    while (true) {
+      const int slot = wq * kRetDepth + rq.stage;
+      bool k = mbar_wait_bounded(&ret_full[slot], rq.phase, abort_flag, wait_ns);
+      k = __all_sync(0xffffffffu, k);
+      if (!k) {
+        if (lane == 0) report_status(a.status, kGemmAccTimeout, 5, blockIdx.x, 0);
+        break;
+      }
+      const int* d = ret_desc + slot * 4;
+      const int n_rows = d[0], row_start = d[1], mb = d[2];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ret_empty[slot]);
+      rq.advance(kRetDepth);
+      if (n_rows < 0) break;
+      completed += return_rows(a, n_rows, row_start, mb, wq, lane);
+    }
+    return_finish(a, completed, lane);
   }
 
   __syncwarp();
@@ -401,11 +548,11 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-template <bool kGateUp, int N_MAX>
+template <bool kGateUp, int N_MAX, bool kReturn = false>
 static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStream_t stream) {
   using Cfg = GemmCfg<kGateUp, N_MAX>;
   static bool configured = false;
-  auto kern = grouped_gemm_kernel<kGateUp, N_MAX>;
+  auto kern = grouped_gemm_kernel<kGateUp, N_MAX, kReturn>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
@@ -413,7 +560,8 @@ static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStre
   }
   CUtensorMap tm;
   memcpy(&tm, tmap, sizeof(tm));
-  return (int)launch_kernel(kern, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, true, tm, *args);
+  const int threads = kReturn ? kThreadsWithReturn : kThreads;
+  return (int)launch_kernel(kern, dim3(grid), dim3(threads), Cfg::kSmemBytes, stream, true, tm, *args);
 }
 
 static int check_args(const mf_gemm_args* a, int n_max, int grid) {
@@ -471,6 +619,11 @@ int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid
   int c = mf::check_args(args, n_max, grid);
   if (c) return c;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (args->ret_peer != nullptr) {  // owner reduce + return push fused into the epilogue (four extra warps)
+    if (n_max == 32) return mf::launch<false, 32, true>(tmap, args, grid, s);
+    if (n_max == 64) return mf::launch<false, 64, true>(tmap, args, grid, s);
+    return mf::launch<false, 128, true>(tmap, args, grid, s);
+  }
   if (n_max == 32) return mf::launch<false, 32>(tmap, args, grid, s);
   if (n_max == 64) return mf::launch<false, 64>(tmap, args, grid, s);
   return mf::launch<false, 128>(tmap, args, grid, s);

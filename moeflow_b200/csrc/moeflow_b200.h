@@ -18,6 +18,7 @@ enum {
   MF_PLAN_SPLIT2 = 2,     // K split of the down GEMM
   MF_PLAN_N_ENTRIES = 3,  // valid (row, slot) entries = offsets[L]
   MF_PLAN_SLOT_COLS = 4,  // token columns per split-K partial slot (multiple of 16; 0 = the kernel's n_max)
+  MF_PLAN_VALID_ROWS = 5, // received rows with at least one hit on this rank
   MF_PLAN_WORDS = 8
 };
 
@@ -51,6 +52,20 @@ typedef struct {
   long long b_scale_pitch;   // floats between rows of b_scale
   float* out_scale;          // reserved
   unsigned long long* trace; // optional [grid, 8] globaltimer stamps per CTA (profiling aid), or NULL
+  // Down GEMM only, optional (ret_peer != NULL): owner reduce + return all-to-all fused into the epilogue.
+  // When the last of a received row's slots has been written for a 32-column quarter of a block, that
+  // warp sums the row's slots in slot order (fp32, from +0.0) and stores the bf16 partial straight into
+  // the source rank's ret_recv[this rank, t]; the warp that completes the last quarter publishes the
+  // return flags.  Needs the plan word MF_PLAN_VALID_ROWS and row_hits from mf_expert_meta.
+  const unsigned long long* ret_peer;   // [R] base addresses of every rank's ret_recv [R, C, H]
+  const unsigned long long* ret_flag;   // [R] base addresses of every rank's return flags [R]
+  const unsigned* ret_epoch;
+  unsigned* ret_done;        // completion counter, zero between launches
+  int* row_cnt;              // [rows * m_blocks * 4] arrival counters, zero between launches (self-cleaning)
+  const int* row_hits;       // [rows] valid slots of each received row on this rank
+  const int* entry_row;      // [entries] received row of every expert-major entry
+  const int* inv;            // [rows * top_k] (row, slot) -> entry, -1 = none
+  int ret_rank, ret_R, ret_C, ret_K;
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
@@ -153,6 +168,7 @@ typedef struct {
   unsigned long long* status;
   unsigned long long wait_ns;
   long long partial_floats;  // capacity of the split-K scratch in floats: bounds slots = floats / (tiles * cols * 128)
+  int* row_hits;             // optional [rows]: valid slots per received row (for the fused return path)
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 

@@ -13,7 +13,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libmoeflow_b200.so"
 
-PLAN_N_TILES, PLAN_SPLIT1, PLAN_SPLIT2, PLAN_N_ENTRIES, PLAN_SLOT_COLS, PLAN_WORDS = 0, 1, 2, 3, 4, 8
+PLAN_N_TILES, PLAN_SPLIT1, PLAN_SPLIT2, PLAN_N_ENTRIES, PLAN_SLOT_COLS, PLAN_VALID_ROWS, PLAN_WORDS = 0, 1, 2, 3, 4, 5, 8
 
 STATUS_NAMES = {
     0: "ok",
@@ -57,6 +57,18 @@ class GemmArgs(C.Structure):
         ("b_scale_pitch", C.c_longlong),
         ("out_scale", C.c_void_p),
         ("trace", C.c_void_p),
+        ("ret_peer", C.c_void_p),
+        ("ret_flag", C.c_void_p),
+        ("ret_epoch", C.c_void_p),
+        ("ret_done", C.c_void_p),
+        ("row_cnt", C.c_void_p),
+        ("row_hits", C.c_void_p),
+        ("entry_row", C.c_void_p),
+        ("inv", C.c_void_p),
+        ("ret_rank", C.c_int),
+        ("ret_R", C.c_int),
+        ("ret_C", C.c_int),
+        ("ret_K", C.c_int),
     ]
 
 
@@ -128,6 +140,7 @@ class MetaArgs(C.Structure):
         ("status", C.c_void_p),
         ("wait_ns", C.c_ulonglong),
         ("partial_floats", C.c_longlong),
+        ("row_hits", C.c_void_p),
     ]
 
 

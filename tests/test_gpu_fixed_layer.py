@@ -103,6 +103,29 @@ def test_expert_meta_matches_torch_layout(world, cap):
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("dist", ["uniform", "hotspot"])
+def test_fused_return_path_equals_separate_kernel_bitwise(world, dist):
+    """Owner reduce + return push inside the down GEMM gives the same bytes as the separate kernel."""
+    cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4, moe_intermediate_size=256)
+    cap = 16
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    tokens = [cap, 7, 0, 3][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 33, dist)
+    sep = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"fuse_return": False})
+    fus = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"fuse_return": True})
+    for _ in range(3):  # repeated forwards: the arrival counters must clean themselves
+        out_s = [o.clone() for o in simulate_fixed(sep, xs, lgs, bias)]
+        out_f = [o.clone() for o in simulate_fixed(fus, xs, lgs, bias)]
+        torch.cuda.synchronize()
+        for r in range(world):
+            _ok(fus[r])
+            assert bitwise_equal(out_f[r], out_s[r])
+            hit = fus[r].hit.bool().t()
+            assert bitwise_equal(fus[r].ret_recv[hit], sep[r].ret_recv[hit])
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("dist", ["uniform", "zipf", "hotspot"])
 def test_layer_matches_oracle_and_twin(world, dist):
     cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4, moe_intermediate_size=256)
