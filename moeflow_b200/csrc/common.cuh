@@ -76,6 +76,15 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
 __device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Publish one value in word [rank] of every peer's flag array.  A release store carries a full
+// system-scope fence each; with R peers that is R fences in a row, so fence once and store relaxed.
+__device__ __forceinline__ void publish_flags(const unsigned long long* peer_flag, int n_peers, int rank, unsigned value) {
+  __threadfence_system();
+  for (int d = 0; d < n_peers; ++d) st_relaxed_sys_u32(reinterpret_cast<unsigned*>(peer_flag[d]) + rank, value);
+}
 __device__ __forceinline__ unsigned ld_relaxed_sys_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

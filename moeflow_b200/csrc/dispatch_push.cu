@@ -111,11 +111,9 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
   if (tid == 0) {
     const unsigned done = atomicAdd(a.done_counter, 1u);
     if (done == gridDim.x - 1) {
-      __threadfence_system();
       *a.done_counter = 0u;
       *a.epoch = epoch_next;
-      for (int d = 0; d < a.R; ++d)
-        st_release_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, epoch_next);
+      publish_flags(a.peer_flag, a.R, a.rank, epoch_next);
     }
   }
 }

@@ -139,10 +139,8 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
     const unsigned total = (unsigned)a.plan[MF_PLAN_VALID_ROWS] * (unsigned)a.m_blocks * 4u;
     const unsigned before = atomicAdd(a.ret_done, (unsigned)completed);
     if (before + (unsigned)completed == total) {
-      __threadfence_system();
       *a.ret_done = 0u;
-      const unsigned epoch = *a.ret_epoch;
-      for (int d = 0; d < a.ret_R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.ret_flag[d]) + a.ret_rank, epoch);
+      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch);
     }
   }
 }
@@ -221,8 +219,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
     // Fused return path with nothing to return: the flags must still be published (thread 64 belongs to
     // the warps that waited for the previous kernel).
     if (a.plan[MF_PLAN_VALID_ROWS] == 0) {
-      const unsigned epoch = *a.ret_epoch;
-      for (int d = 0; d < a.ret_R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.ret_flag[d]) + a.ret_rank, epoch);
+      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch);
     }
   }
   const int n_tiles = a.plan[MF_PLAN_N_TILES];

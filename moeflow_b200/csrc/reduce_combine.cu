@@ -79,10 +79,8 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   if (tid == 0) {
     const unsigned done = atomicAdd(a.done_counter, 1u);
     if (done == gridDim.x - 1) {
-      __threadfence_system();
       *a.done_counter = 0u;
-      const unsigned epoch = *a.epoch;
-      for (int d = 0; d < a.R; ++d) st_release_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, epoch);
+      publish_flags(a.peer_flag, a.R, a.rank, *a.epoch);
     }
   }
 }
