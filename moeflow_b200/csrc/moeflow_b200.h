@@ -200,6 +200,12 @@ typedef struct {
 } mf_combine_args;
 int mf_combine(const mf_combine_args* args, mf_stream_t stream);
 
+// ---- received-row unpacking for external expert kernels ------------------------------------------------
+// rows [n_rows, pitch bytes] -> hidden [n_rows, H] bf16, ids [n_rows, K] (exactly one of ids32 / ids64) and
+// weights [n_rows, K] fp32; empty slots and rows with valid = 0 get `filler` and weight 0.
+int mf_expert_prepare(const void* rows, long long pitch, int n_rows, int H, int K, int rank_offset, int filler,
+                      void* hidden, int* ids32, long long* ids64, float* weights, mf_stream_t stream);
+
 // ---- activation quantisation (1x128 groups -> e4m3 + fp32 scales) --------------------------------------
 // q[r, :] = e4m3(x[src(r), :] / scale), scales[r, g] = max(amax_g, 1e-10) / 448 for every 128-wide group g.
 // src(r) = row_index ? row_index[r] : r.  With valid_off >= 0 a source row whose int32 at that byte offset is

@@ -161,3 +161,45 @@ int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, in
 }
 
 }  // extern "C"
+
+// -------------------------------------------------------------------------------------------------
+// Received-row unpacking for external expert kernels: rows [N, pitch] -> contiguous hidden [N, H],
+// global expert ids [N, K] (filler expert where the slot is empty or the row is not valid) and
+// fp32 weights [N, K] (0 there).  One CTA per row.  Counterpart of the reference's
+// moeflow/kernels/expert_prepare.py:10-75.
+// -------------------------------------------------------------------------------------------------
+namespace mf {
+__global__ void __launch_bounds__(kRowThreads)
+expert_prepare_kernel(const uint8_t* __restrict__ rows, long long pitch, int H, int K, int rank_offset, int filler,
+                      uint4* __restrict__ hidden, int* __restrict__ ids32, long long* __restrict__ ids64,
+                      float* __restrict__ weights) {
+  grid_dep_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const uint8_t* row = rows + (size_t)r * pitch;
+  const int* meta = reinterpret_cast<const int*>(row + (size_t)H * 2);
+  const bool valid = meta[2 * K] != 0;
+  if (tid < K) {
+    const int local = meta[tid];
+    const bool live = valid && local >= 0;
+    const int gid = live ? local + rank_offset : filler;
+    if (ids32) ids32[(size_t)r * K + tid] = gid;
+    if (ids64) ids64[(size_t)r * K + tid] = gid;
+    weights[(size_t)r * K + tid] = live ? __int_as_float(meta[K + tid]) : 0.f;
+  }
+  const int chunks = H / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(row);
+  uint4* dst = hidden + (size_t)r * chunks;
+  // Rows that are not valid may hold stale payload (even NaN): copy them as they are; their slots all
+  // point at the filler expert with weight 0, so nothing of them reaches an output.
+  for (int c = tid; c < chunks; c += kRowThreads) dst[c] = src[c];
+}
+}  // namespace mf
+
+extern "C" int mf_expert_prepare(const void* rows, long long pitch, int n_rows, int H, int K, int rank_offset, int filler,
+                                 void* hidden, int* ids32, long long* ids64, float* weights, mf_stream_t stream) {
+  if (n_rows == 0) return 0;
+  if (H % 8 != 0 || K > 32 || (pitch & 15) != 0 || (ids32 == nullptr) == (ids64 == nullptr)) return -1;
+  return (int)mf::launch_kernel(mf::expert_prepare_kernel, dim3(n_rows), dim3(mf::kRowThreads), 0,
+                                static_cast<cudaStream_t>(stream), true, static_cast<const uint8_t*>(rows), pitch, H, K,
+                                rank_offset, filler, static_cast<uint4*>(hidden), ids32, ids64, weights);
+}

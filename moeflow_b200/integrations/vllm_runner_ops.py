@@ -35,6 +35,23 @@ def prepare_expert_inputs(rows: torch.Tensor, hidden_size: int, top_k: int, rank
     0, so garbage (NaN) in the hidden lanes or weights of such rows never reaches an output.
     """
     n = rows.shape[0]
+    if rows.is_cuda and rows.dtype == torch.bfloat16 and rows.stride(1) == 1 and ids_dtype in (torch.int32, torch.int64):
+        from ..ops import _lib
+
+        if _lib.available() and (rows.stride(0) * 2) % 16 == 0 and rows.data_ptr() % 16 == 0:
+            # one sm_100a kernel instead of a chain of PyTorch ops
+            hidden = torch.empty(n, hidden_size, dtype=torch.bfloat16, device=rows.device)
+            gids = torch.empty(n, top_k, dtype=ids_dtype, device=rows.device)
+            weights = torch.empty(n, top_k, dtype=torch.float32, device=rows.device)
+            is32 = ids_dtype == torch.int32
+            _lib.check(
+                _lib.lib().mf_expert_prepare(rows.data_ptr(), rows.stride(0) * 2, n, hidden_size, top_k, rank_offset,
+                                             filler_expert(rank_offset, num_experts), hidden.data_ptr(),
+                                             gids.data_ptr() if is32 else None, None if is32 else gids.data_ptr(),
+                                             weights.data_ptr(), _lib.stream_ptr()),
+                "expert_prepare",
+            )
+            return hidden, gids, weights
     lanes = (4 * (2 * top_k + 1) + rows.element_size() - 1) // rows.element_size()
     meta = rows[:, hidden_size : hidden_size + lanes].contiguous().view(torch.int32)[:, : 2 * top_k + 1]
     valid = meta[:, 2 * top_k] != 0

@@ -217,6 +217,7 @@ def lib() -> C.CDLL:
         "mf_expert_meta": [C.POINTER(MetaArgs), P],
         "mf_owner_reduce_push": [C.POINTER(ReducePushArgs), P],
         "mf_combine": [C.POINTER(CombineArgs), P],
+        "mf_expert_prepare": [P, LL, I, I, I, I, I, P, P, P, P, P],
         "mf_peer_alloc": [C.POINTER(P), ULL],
         "mf_peer_free": [P],
         "mf_peer_export": [P, P],

@@ -258,3 +258,86 @@ def test_graph_replay_with_changing_inputs(world):
                 err = normwise_rel_err(cu[r].out[:n], ref[r][:n].float())
                 assert err < 4 * 2.0**-8, (it, r, err)
     del g_pack, g_exp, g_comb
+
+
+@pytest.mark.parametrize("ids_dtype", [torch.int32, torch.int64])
+def test_expert_prepare_kernel_matches_torch_and_ignores_poisoned_rows(ids_dtype):
+    """Received-row unpacking for external experts: kernel == PyTorch definition, NaN payload in invalid rows is inert."""
+    from moeflow_b200.integrations.vllm_runner_ops import prepare_expert_inputs
+
+    cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4)
+    world, cap = 2, 8
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    xs, lgs = _inputs(cfg, world, [cap, 3], 77)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    for ly, x, lg in zip(cu, xs, lgs):
+        ly.stage_pack(x, lg, None)
+    torch.cuda.synchronize()
+    ly = cu[1]
+    meta = ly._meta_view(ly._recv_store)
+    invalid = meta[:, :, 2 * cfg.top_k] == 0
+    ly._recv_store[:, :, : cfg.hidden_size][invalid] = float("nan")
+    rows = ly._recv_store.view(world * cap, ly.pitch)[:, : ly.row_width]
+    off = ly.rank * ly.L
+    h, ids, w = prepare_expert_inputs(rows, cfg.hidden_size, cfg.top_k, off, cfg.n_routed_experts, ids_dtype)
+    h_t, ids_t, w_t = prepare_expert_inputs(rows.cpu(), cfg.hidden_size, cfg.top_k, off, cfg.n_routed_experts, ids_dtype)
+    torch.cuda.synchronize()
+    assert ids.dtype == ids_dtype and torch.equal(ids.cpu(), ids_t) and bitwise_equal(w.cpu(), w_t)
+    valid_rows = (~invalid).reshape(-1).cpu()
+    assert bitwise_equal(h.cpu()[valid_rows], h_t[valid_rows])
+    assert (w.cpu()[~valid_rows] == 0).all() and (ids.cpu()[~valid_rows] == (0 if off else cfg.n_routed_experts - 1)).all()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+@pytest.mark.parametrize("mode", ["plain", "prepared", "direct"])
+def test_external_expert_function_on_the_cuda_backend(world, mode):
+    """expert_fn / prepare_fn / direct output hooks: peer-memory transport around externally computed partial rows."""
+    from moeflow_b200.integrations.vllm_runner_ops import make_combine_fn, make_prepare_fn
+
+    cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=2)
+    cap = 8
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    tokens = [cap, 5][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 55)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    tw = _layers(cfg, world, cap, w13, w2, "torch")
+
+    def expert_fn(hidden, ids, weights):
+        # stand-in for an engine's fused experts: every hit contributes weight * hidden
+        return (hidden.float() * weights.sum(-1, keepdim=True)).to(hidden.dtype).contiguous()
+
+    outs = {}
+    for name, layers in (("cuda", cu), ("torch", tw)):
+        routed = [layers[0].stage_route(lg, None) if name == "torch" else cu[r].stage_route(lg, None) for r, lg in enumerate(lgs)]
+        routed = [(w.clone(), i.clone()) for w, i in routed]
+        hits = [ly.stage_dispatch_pack(x, w, i).clone() for ly, x, (w, i) in zip(layers, xs, routed)]
+        if name == "torch":
+            for d in range(world):
+                for s in range(world):
+                    layers[d]._recv_store[s].copy_(layers[s]._send_store[d])
+        for r, ly in enumerate(layers):
+            prep = make_prepare_fn(cfg, r * ly.L, cfg.n_routed_experts, torch.int32) if mode != "plain" else None
+            got = ly.stage_experts(expert_fn, prepare_fn=prep, direct_output=(mode == "direct"))
+            if mode == "direct":
+                assert got is not None and got.shape == (world, cap, cfg.hidden_size)
+                if name == "cuda":
+                    ly._cuda_push_partials(got.view(world * cap, cfg.hidden_size))
+                else:
+                    ly.ret_send.copy_(got)
+        if name == "torch":
+            for d in range(world):
+                for s in range(world):
+                    layers[d].ret_recv[s].copy_(layers[s].ret_send[d])
+        outs[name] = [ly.stage_combine(h, torch.bfloat16).clone() for ly, h in zip(layers, hits)]
+        torch.cuda.synchronize()
+    for r in range(world):
+        _ok(cu[r])
+        assert bitwise_equal(outs["cuda"][r], outs["torch"][r])
+    # adapter combine on the cuda backend: wait for the return flags, then the ring kernel
+    ring = make_combine_fn("bf16_ring_fused", 0)
+    cu[0]._cuda_wait_return()
+    got = ring(cu[0].ret_recv, cu[0].hit)
+    from moeflow_b200.fixed import combine_partials
+
+    torch.cuda.synchronize()
+    assert bitwise_equal(got, combine_partials(cu[0].ret_recv, cu[0].hit, torch.bfloat16, 0, "bf16_ring"))
