@@ -23,7 +23,7 @@ from ..config import MoEConfig
 from ..ep_moe import EPMoELayer
 from ..fixed import FixedEPLayer
 
-BACKENDS = ("fused", "torch_fixed", "naive", "reference_fixed")
+BACKENDS = ("fused", "torch_fixed", "naive", "naive_tcgen05", "fixed_vllm_experts", "reference_fixed")
 
 
 @dataclass
@@ -90,6 +90,51 @@ class NaiveBackend:
         return self.layer.forward(x, logits, self.bias, self.comm)
 
 
+class NaiveTcgen05Backend(NaiveBackend):
+    """Variable-size pipeline over the collective transport, experts on the tcgen05 grouped GEMMs."""
+
+    name = "naive_tcgen05"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity=None, **_):
+        from ..experts import Tcgen05GroupedExperts
+
+        self.layer = EPMoELayer(cfg, info.rank, info.world, w13_local, w2_local, experts=Tcgen05GroupedExperts())
+        self.comm = CollectiveRowExchange()
+        self.bias = bias
+
+
+class FixedVllmExpertsBackend:
+    """Fused peer-memory transport around the serving engine's own bf16 fused-experts kernel.
+
+    Same router and transport as ``fused``; only the expert GEMMs differ (vLLM's ``fused_experts``), so an
+    A/B against ``fused`` isolates the expert kernels and one against the engine's native all-gather /
+    reduce-scatter isolates the transport.  Needs an importable vLLM; library code, comparison arm only.
+    """
+
+    name = "fixed_vllm_experts"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity, **layer_kw):
+        from vllm.model_executor.layers.fused_moe import fused_experts  # noqa: F401 - fails early without vLLM
+
+        self._fused_experts = fused_experts
+        self.cfg, self.bias, self.w13, self.w2 = cfg, bias, w13_local, w2_local
+        self.layer = FixedEPLayer(cfg, info.rank, info.world, None, None, capacity=capacity, backend="cuda",
+                                  device=w13_local.device, dtype=w13_local.dtype, **layer_kw)
+
+    def _experts(self, hidden, local_ids, weights):
+        # absent slots: expert 0 with weight 0; rows without any hit may hold stale payload, so zero them
+        live = local_ids >= 0
+        x = torch.where(live.any(dim=-1, keepdim=True), hidden, torch.zeros_like(hidden))
+        ids = torch.where(live, local_ids, torch.zeros_like(local_ids)).to(torch.int32)
+        w = torch.where(live, weights, torch.zeros_like(weights))
+        # the engine's SiLU-and-mul has no clamp; with a finite swiglu_limit the two arms differ where it bites
+        return self._fused_experts(x.contiguous(), self.w13, self.w2, w, ids)
+
+    def run(self, x, logits):
+        w, ids = self.layer.stage_route(logits, self.bias)
+        return self.layer.forward_routed(x, w, ids, expert_fn=self._experts)[: x.shape[0]]
+
+
 class ReferenceFixedBackend:
     """The reference's own fixed layer with all four of its fusion switches (Triton + NCCL)."""
 
@@ -115,6 +160,7 @@ class ReferenceFixedBackend:
 
 def make_backend(name: str, *args, **kw):
     table = {"fused": FusedFixedBackend, "torch_fixed": TorchFixedBackend, "naive": NaiveBackend,
+             "naive_tcgen05": NaiveTcgen05Backend, "fixed_vllm_experts": FixedVllmExpertsBackend,
              "reference_fixed": ReferenceFixedBackend}
     if name not in table:
         raise ValueError(f"unknown backend {name!r}; choose from {BACKENDS}")

@@ -82,4 +82,26 @@ class BatchedTorchExperts:
         return y.to(a.dtype)
 
 
-EXPERT_BACKENDS = {"torch_loop": TorchLoopExperts, "torch_bmm": BatchedTorchExperts}
+class Tcgen05GroupedExperts:
+    """The sm_100a grouped GEMMs (gate/up + SwiGLU, down + routing weight) behind the ExpertCompute
+    protocol of the variable-size pipeline.  The tile plan is built from the offsets on the host (this
+    pipeline synchronises with the host anyway); ``FixedEPLayer`` drives the same kernels with a
+    device-side plan instead."""
+
+    name = "tcgen05_grouped"
+
+    def __init__(self, block_m: int = 64):
+        self.block_m = block_m
+
+    def __call__(self, a, expert_offsets, w13, w2, swiglu_limit, row_weight=None):
+        from .ops.grouped_gemm import down_proj, gate_up_swiglu, plan_from_offsets
+
+        if a.shape[0] == 0:
+            return torch.empty_like(a)
+        tp = plan_from_offsets(expert_offsets, self.block_m, a.device)
+        act = gate_up_swiglu(a.contiguous(), w13, tp, limit=swiglu_limit)
+        scale = None if row_weight is None else row_weight.to(torch.float32).contiguous()
+        return down_proj(act, w2, tp, row_scale=scale)
+
+
+EXPERT_BACKENDS = {"torch_loop": TorchLoopExperts, "torch_bmm": BatchedTorchExperts, "tcgen05_grouped": Tcgen05GroupedExperts}

@@ -134,3 +134,20 @@ def test_glm_shape_one_expert_tile():
     ref_act = _ref_gate_up(x, row_index[:n], w13, offsets, 10.0)
     assert normwise_rel_err(act, ref_act) < 4 * 2.0**-8
     assert normwise_rel_err(y, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_expert_compute_backend_matches_the_torch_loop(weighted):
+    """The ExpertCompute adapter of the variable-size pipeline: same call, tcgen05 kernels inside."""
+    from moeflow_b200.experts import EXPERT_BACKENDS
+
+    w13, w2, x, _, offsets, scale = _problem([5, 0, 70, 17], 512, 256, seed=11)
+    n = offsets[-1]
+    a = x[:n].contiguous() if x.shape[0] >= n else x
+    offs = torch.tensor(offsets, dtype=torch.int64, device=x.device)
+    rw = scale[:n] if weighted else None
+    got = EXPERT_BACKENDS["tcgen05_grouped"]()(a, offs, w13, w2, 10.0, rw)
+    ref = EXPERT_BACKENDS["torch_loop"]()(a.float(), offs, w13.float(), w2.float(), 10.0, rw)
+    torch.cuda.synchronize()
+    assert got.shape == a.shape and got.dtype == a.dtype
+    assert normwise_rel_err(got, ref) < 6 * 2.0**-8, normwise_rel_err(got, ref)
