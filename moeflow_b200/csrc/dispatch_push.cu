@@ -105,10 +105,11 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
     }
   }
 
-  // Publish: every thread's stores are fenced at system scope, then the CTA counts itself done.
-  __threadfence_system();
+  // Publish: the barrier orders every thread's stores before thread 0's system fence (cumulative), then
+  // the CTA counts itself done.
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const unsigned done = atomicAdd(a.done_counter, 1u);
     if (done == gridDim.x - 1) {
       *a.done_counter = 0u;

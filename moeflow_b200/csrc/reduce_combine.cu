@@ -74,9 +74,11 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
       dst[c] = pack_bf16x8(acc);
     }
   }
-  __threadfence_system();
+  // The barrier orders every thread's stores before thread 0's fence, which is cumulative: one system
+  // fence per CTA instead of one per thread.
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const unsigned done = atomicAdd(a.done_counter, 1u);
     if (done == gridDim.x - 1) {
       *a.done_counter = 0u;
