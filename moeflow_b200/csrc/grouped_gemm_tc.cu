@@ -46,8 +46,9 @@ struct GemmCfg {
   static constexpr int kStageA = kATiles * kTileBytesA;
   static constexpr int kStageB = N_MAX * 128;
   static constexpr int kStageBytes = kStageA + kStageB;
-  // keep the pipeline under ~200 KB of the 227 KB a CTA may use
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  // As many stages as fit in 216 KB of the 227 KB a CTA may use (2 KB more go to alignment slack and
+  // barriers): the bytes in flight per SM, not the tensor pipe, bound these weight-streaming kernels.
+  static constexpr int kStages = (216 * 1024) / kStageBytes > 10 ? 10 : (216 * 1024) / kStageBytes;
   static constexpr int kAccCols = kATiles * N_MAX;
   static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128}
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/;

@@ -421,8 +421,10 @@ class FixedEPLayer:
         i32 = dict(dtype=torch.int32, device=dev)
         N = self.n_entries
         # token rows per tile: 64 for decode; 128 when experts see many rows (prefill), which halves the
-        # number of times an expert's weights are streamed
-        rows_per_expert = (R * Cc * K) / max(L, 1)
+        # number of times an expert's weights are streamed.  The estimate is the expectation under even
+        # routing (R*C*K entries over R*L experts), not the worst case: wide tiles cost pipeline stages, and
+        # with few rows per expert the narrower tile keeps more weight bytes in flight.
+        rows_per_expert = (Cc * K) / max(L, 1)
         self.block_m = int(self.gemm_kwargs.get("block_m", 128 if rows_per_expert >= 96 else 64))
         if self.block_m not in (32, 64, 128):
             raise ValueError("block_m must be 32, 64 or 128")
