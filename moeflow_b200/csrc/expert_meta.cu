@@ -23,6 +23,7 @@ namespace mf {
 
 constexpr int kMetaThreads = 1024;
 constexpr int kMetaWarps = kMetaThreads / 32;
+constexpr int kMetaBatch = 8;  // warp-wide steps whose loads are issued together
 
 // Exclusive scan of one int per thread over the whole block; `total` gets the sum.
 __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
@@ -102,19 +103,39 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   const size_t meta_off = (size_t)a.H * 2;
   int* my_hist = hist + warp * L;
 
-  // sweep 1: per-warp histogram
-  for (int i0 = begin; i0 < end; i0 += 32) {
-    const int i = i0 + lane;
-    int key = -1;
-    if (i < end) {
-      const int row = i / K, slot = i - row * K;
-      const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
-      const int id = meta[slot];
-      if (meta[2 * K] != 0 && id >= 0 && id < L) key = id;
+  // Keys of a batch of kMetaBatch warp-wide steps are loaded together (independent loads in flight at
+  // once) before the dependent match/count steps: the received rows are cold in cache when this kernel
+  // starts, and one load latency per step would dominate it.
+  auto load_keys = [&](int i0, int (&key)[kMetaBatch], int (&wbits)[kMetaBatch], bool want_w) {
+#pragma unroll
+    for (int b = 0; b < kMetaBatch; ++b) {
+      const int i = i0 + b * 32 + lane;
+      key[b] = -1;
+      wbits[b] = 0;
+      if (i < end) {
+        const int row = i / K, slot = i - row * K;
+        const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
+        const int id = meta[slot];
+        const int valid = meta[2 * K];
+        const int wb = want_w ? meta[K + slot] : 0;
+        if (valid != 0 && id >= 0 && id < L) {
+          key[b] = id;
+          wbits[b] = wb;
+        }
+      }
     }
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    if (key >= 0 && lane == __ffs(same) - 1) my_hist[key] += __popc(same);
-    __syncwarp();
+  };
+
+  // sweep 1: per-warp histogram
+  for (int i0 = begin; i0 < end; i0 += 32 * kMetaBatch) {
+    int key[kMetaBatch], wbits[kMetaBatch];
+    load_keys(i0, key, wbits, false);
+#pragma unroll
+    for (int b = 0; b < kMetaBatch; ++b) {
+      const unsigned same = __match_any_sync(0xffffffffu, key[b]);
+      if (key[b] >= 0 && lane == __ffs(same) - 1) my_hist[key[b]] += __popc(same);
+      __syncwarp();
+    }
   }
   __syncthreads();
 
@@ -192,36 +213,31 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   __syncthreads();
 
   // sweep 2: place the entries
-  for (int i0 = begin; i0 < end; i0 += 32) {
-    const int i = i0 + lane;
-    int key = -1, row = 0, slot = 0, wbits = 0;
-    if (i < end) {
-      row = i / K;
-      slot = i - row * K;
-      const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
-      const int id = meta[slot];
-      if (meta[2 * K] != 0 && id >= 0 && id < L) {
-        key = id;
-        wbits = meta[K + slot];
+  for (int i0 = begin; i0 < end; i0 += 32 * kMetaBatch) {
+    int key[kMetaBatch], wbits[kMetaBatch];
+    load_keys(i0, key, wbits, true);
+#pragma unroll
+    for (int b = 0; b < kMetaBatch; ++b) {
+      const int i = i0 + b * 32 + lane;
+      const unsigned same = __match_any_sync(0xffffffffu, key[b]);
+      if (key[b] >= 0) {
+        // pos < N always holds when the rows did not change between the two sweeps; the guard keeps a
+        // racing writer (a peer that runs ahead in a truncated stage-timing run) from causing a stray store.
+        const int pos = offs[key[b]] + my_hist[key[b]] + __popc(same & ((1u << lane) - 1u));
+        if (pos < N) {
+          const int row = i / K;
+          a.entry_row[pos] = row;
+          a.entry_slot[pos] = i - row * K;
+          a.entry_w[pos] = __int_as_float(wbits[b]);
+        }
+        a.inv[i] = pos < N ? pos : -1;
+      } else if (i < end) {
+        a.inv[i] = -1;
       }
+      __syncwarp();
+      if (key[b] >= 0 && lane == __ffs(same) - 1) my_hist[key[b]] += __popc(same);
+      __syncwarp();
     }
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    if (key >= 0) {
-      // pos < N always holds when the rows did not change between the two sweeps; the guard keeps a
-      // racing writer (a peer that runs ahead in a truncated stage-timing run) from causing a stray store.
-      const int pos = offs[key] + my_hist[key] + __popc(same & ((1u << lane) - 1u));
-      if (pos < N) {
-        a.entry_row[pos] = row;
-        a.entry_slot[pos] = slot;
-        a.entry_w[pos] = __int_as_float(wbits);
-      }
-      a.inv[i] = pos < N ? pos : -1;
-    } else if (i < end) {
-      a.inv[i] = -1;
-    }
-    __syncwarp();
-    if (key >= 0 && lane == __ffs(same) - 1) my_hist[key] += __popc(same);
-    __syncwarp();
   }
 }
 

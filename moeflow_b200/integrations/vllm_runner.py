@@ -100,6 +100,7 @@ class RunnerCore:
         self._moeflow_fixed_calls = 0
         self._routing_trace_calls = 0
         self._local_kernel = None
+        self._router_takes_dtype = None
         self._native_tmaps = None
         self._fixed_probe = None
         if self.moeflow.validate_fixed:
@@ -168,7 +169,39 @@ class RunnerCore:
         return fixed_capacity(local_tokens, None if across is None else across.tolist(), self.moeflow.max_tokens)
 
     def _is_monolithic(self) -> bool:
-        return bool(self.routed_experts.quant_method.is_monolithic)
+        method = getattr(self.routed_experts, "quant_method", None) or self._quant_method
+        return bool(method.is_monolithic)
+
+    def _select_experts(self, hidden_states, router_logits, input_ids):
+        """The engine's own router.  Engines differ in whether ``select_experts`` takes the id dtype."""
+        import inspect
+
+        dtype = self._quant_method.topk_indices_dtype
+        if self._router_takes_dtype is None:
+            try:
+                params = inspect.signature(self.router.select_experts).parameters
+                self._router_takes_dtype = "topk_indices_dtype" in params or any(
+                    p.kind is p.VAR_KEYWORD for p in params.values())
+            except (TypeError, ValueError):
+                self._router_takes_dtype = True
+        if self._router_takes_dtype:
+            return self.router.select_experts(hidden_states=hidden_states, router_logits=router_logits,
+                                              topk_indices_dtype=dtype, input_ids=input_ids)
+        weights, ids = self.router.select_experts(hidden_states=hidden_states, router_logits=router_logits,
+                                                  input_ids=input_ids)
+        return weights, (ids if dtype is None else ids.to(dtype))
+
+    def _run_modular(self, hidden_states, weights, ids, shared_experts_input):
+        """The engine's modular expert path with routing already decided."""
+        experts = self.routed_experts
+        if hasattr(experts, "forward_modular"):
+            return experts.forward_modular(x=hidden_states, topk_weights=weights, topk_ids=ids,
+                                           shared_experts=self._shared_experts, shared_experts_input=shared_experts_input)
+        return self._quant_method.apply(layer=experts, x=hidden_states, topk_weights=weights, topk_ids=ids,
+                                        shared_experts=self._shared_experts, shared_experts_input=shared_experts_input)
+
+    def _late_shared_experts(self) -> None:
+        """Hook for engines that run the shared experts after the routed ones on a second stream."""
 
     def _apply_quant_method(self, hidden_states, router_logits, shared_experts_input, input_ids=None,
                             shared_experts_overlapping=False):
@@ -190,6 +223,8 @@ class RunnerCore:
     def _shared_output(self, overlapping: bool, routed_out):
         if overlapping:
             self._shared_experts.wait()
+        else:
+            self._late_shared_experts()
         shared = self._shared_experts.output if self._shared_experts is not None else None
         return shared, routed_out
 
@@ -201,14 +236,10 @@ class RunnerCore:
         weights, ids = route(router_logits, bias, self.moeflow_cfg)
         self._record_routing_trace(ids, weights)
         if self._moeflow_log is not None and self._moeflow_calls <= MAX_LOGGED_CALLS_PER_LAYER:
-            v_w, v_ids = self.router.select_experts(hidden_states=hidden_states, router_logits=router_logits,
-                                                    topk_indices_dtype=self._quant_method.topk_indices_dtype,
-                                                    input_ids=input_ids)
+            v_w, v_ids = self._select_experts(hidden_states, router_logits, input_ids)
             self._record(compare_routing(ids, weights, v_ids, v_w))
         ids = ids.to(self._quant_method.topk_indices_dtype or torch.int32)
-        out = self.routed_experts.forward_modular(x=hidden_states, topk_weights=weights, topk_ids=ids,
-                                                  shared_experts=self._shared_experts,
-                                                  shared_experts_input=shared_experts_input)
+        out = self._run_modular(hidden_states, weights, ids, shared_experts_input)
         return self._shared_output(overlapping, out)
 
     # ---- fixed -------------------------------------------------------------------------------------
@@ -241,9 +272,7 @@ class RunnerCore:
     def _apply_fixed(self, hidden_states, router_logits, shared_experts_input, input_ids, overlapping, capacity):
         self._moeflow_fixed_calls += 1
         self._maybe_apply_shared_experts(shared_experts_input, _no_overlap_order())
-        weights, ids = self.router.select_experts(hidden_states=hidden_states, router_logits=router_logits,
-                                                  topk_indices_dtype=self._quant_method.topk_indices_dtype,
-                                                  input_ids=input_ids)
+        weights, ids = self._select_experts(hidden_states, router_logits, input_ids)
         self._record_routing_trace(ids, weights)
         group = self._ep()
         layer = shared_fixed_layer(self.moeflow_cfg, group.rank_in_group, group.world_size, capacity,
@@ -301,16 +330,49 @@ _RUNNER_CLASS = None
 
 
 def _build_runner_class():
+    """Subclass the installed engine's ``MoERunner``.
+
+    Two generations of the runner interface are supported.  The older one calls
+    ``_apply_quant_method(hidden_states, router_logits, shared_experts_input, input_ids, overlapping)`` and keeps
+    the expert layer in ``self.routed_experts``.  The newer one (vLLM 0.22) passes the expert layer as the first
+    argument ``layer``, has no overlap flag and runs multi-stream shared experts after the routed ones.
+    """
+    import inspect
+
     from vllm.config import get_current_vllm_config
     from vllm.model_executor.layers.fused_moe.runner.moe_runner import MoERunner
+
+    takes_layer = "layer" in inspect.signature(MoERunner._apply_quant_method).parameters
 
     class MoEFlowRunner(RunnerCore, MoERunner):
         def __init__(self, *args, **kwargs):
             MoERunner.__init__(self, *args, **kwargs)
             self._moeflow_setup(cfg_from_hf_text_config(get_current_vllm_config().model_config.hf_text_config))
 
-        def _native_apply(self, *args, **kwargs):
-            return MoERunner._apply_quant_method(self, *args, **kwargs)
+        if takes_layer:
+
+            def _apply_quant_method(self, layer, hidden_states, router_logits, shared_experts_input, input_ids=None):
+                # kept out of the module registry on purpose: the layer owns this runner, not the reverse
+                self.__dict__["routed_experts"] = layer
+                self.__dict__["_late_shared_input"] = shared_experts_input
+                return RunnerCore._apply_quant_method(self, hidden_states, router_logits, shared_experts_input, input_ids,
+                                                      False)
+
+            def _native_apply(self, hidden_states, router_logits, shared_experts_input, input_ids=None, *_):
+                return MoERunner._apply_quant_method(self, self.routed_experts, hidden_states, router_logits,
+                                                     shared_experts_input, input_ids)
+
+            def _late_shared_experts(self):
+                from vllm.model_executor.layers.fused_moe.runner.shared_experts import SharedExpertsOrder
+
+                order = getattr(SharedExpertsOrder, "MULTI_STREAM_OVERLAPPED", None)
+                if order is not None:
+                    self._maybe_apply_shared_experts(self.__dict__.get("_late_shared_input"), order)
+
+        else:
+
+            def _native_apply(self, *args, **kwargs):
+                return MoERunner._apply_quant_method(self, *args, **kwargs)
 
     MoEFlowRunner.__qualname__ = "MoEFlowRunner"
     return MoEFlowRunner

@@ -319,3 +319,69 @@ def test_diagnostics_compare_bytes_and_reduction_orders(tmp_path):
         probe.compare(*args, owner_partials=hidden.view(1, 2, 4), experts_per_rank=4, ep_group=group)
     rows = [json.loads(line) for line in next(tmp_path.glob("layer_comparison_*")).read_text().splitlines()]
     assert len(rows) == 2 and rows[0]["bitwise_equal"] and rows[0]["reduction_candidates"]["tested"] > 0
+
+
+def test_router_without_an_id_dtype_argument_and_engine_without_forward_modular(monkeypatch):
+    """The newer runner interface: ``select_experts`` takes no id dtype, the quant method applies the kernel."""
+    monkeypatch.setattr(vllm_runner, "_no_overlap_order", lambda: "NO_OVERLAP")
+    r = _FakeRunner(RunnerSettings(mode="route_check"), None)
+    from moeflow_b200.router import route
+
+    def select_experts(*, hidden_states, router_logits, input_ids=None):
+        w, ids = route(router_logits, None, SMALL)
+        return w, ids.to(torch.int64)
+
+    r.router = SimpleNamespace(select_experts=select_experts)
+    w, ids = r._select_experts(torch.zeros(2, SMALL.hidden_size), torch.randn(2, SMALL.n_routed_experts), None)
+    assert ids.dtype == torch.int32 and r._router_takes_dtype is False
+    applied = {}
+
+    def apply(layer, x, topk_weights, topk_ids, shared_experts, shared_experts_input):
+        applied["layer"] = layer
+        return x * 3
+
+    del r.routed_experts.forward_modular
+    r._quant_method.apply = apply
+    x = torch.ones(2, SMALL.hidden_size)
+    shared, out = r._apply_quant_method(x, torch.randn(2, SMALL.n_routed_experts), None)
+    assert torch.equal(out, x * 3) and applied["layer"] is r.routed_experts
+
+
+def test_runner_class_follows_the_installed_engine_interface(monkeypatch):
+    """Against the importable vLLM: the subclass takes ``layer`` first where the engine's runner does."""
+    pytest.importorskip("vllm")
+    import inspect
+
+    try:
+        from vllm.model_executor.layers.fused_moe.runner.moe_runner import MoERunner
+    except ImportError:
+        pytest.skip("this vLLM has no runner module")
+    cls = vllm_runner.MoEFlowRunner
+    assert issubclass(cls, MoERunner) and cls._moeflow_runner
+    base_params = list(inspect.signature(MoERunner._apply_quant_method).parameters)
+    ours = list(inspect.signature(cls._apply_quant_method).parameters)
+    if "layer" not in base_params:
+        assert ours[:4] == ["self", "hidden_states", "router_logits", "shared_experts_input"]
+        return
+    assert ours[: len(base_params)] == base_params
+    # drive the layer-first entry with stand-ins: a prefill that the fixed mode declines goes to the engine's path
+    runner = cls.__new__(cls)
+    torch.nn.Module.__init__(runner)
+    fake = _FakeRunner(RunnerSettings(mode="fixed", max_tokens=2), [4, 64])
+    for name in ("layer_name", "_quant_method", "_shared_experts", "gate", "router"):
+        runner.__dict__[name] = getattr(fake, name)
+    runner._moeflow_setup(SMALL, RunnerSettings(mode="fixed", max_tokens=2))
+    monkeypatch.setattr(cls, "_forward_context", lambda self: fake._ctx)
+    seen = {}
+
+    def engine_path(self, layer, hidden_states, router_logits, shared_experts_input, input_ids=None):
+        seen["layer"] = layer
+        return None, hidden_states + 1
+
+    monkeypatch.setattr(MoERunner, "_apply_quant_method", engine_path)
+    layer = fake.routed_experts
+    x = torch.zeros(4, SMALL.hidden_size)
+    shared, out = runner._apply_quant_method(layer=layer, hidden_states=x, router_logits=torch.zeros(4, SMALL.n_routed_experts),
+                                             shared_experts_input=None)
+    assert seen["layer"] is layer and runner.routed_experts is layer and torch.equal(out, x + 1)
+    assert "routed_experts" not in dict(runner.named_children())
