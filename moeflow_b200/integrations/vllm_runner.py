@@ -67,14 +67,16 @@ def cfg_from_hf_text_config(hf) -> MoEConfig:
         hidden_size=hf.hidden_size,
         moe_intermediate_size=hf.moe_intermediate_size,
         n_routed_experts=hf.n_routed_experts,
-        n_shared_experts=hf.n_shared_experts,
+        n_shared_experts=getattr(hf, "n_shared_experts", 0) or 0,
         top_k=hf.num_experts_per_tok,
-        n_group=hf.n_group,
-        topk_group=hf.topk_group,
-        norm_topk_prob=hf.norm_topk_prob,
-        routed_scaling_factor=float(hf.routed_scaling_factor),
-        scoring_func=hf.scoring_func,
-        topk_method=hf.topk_method,
+        n_group=getattr(hf, "n_group", 1) or 1,
+        topk_group=getattr(hf, "topk_group", 1) or 1,
+        norm_topk_prob=bool(getattr(hf, "norm_topk_prob", True)),
+        routed_scaling_factor=float(getattr(hf, "routed_scaling_factor", 1.0) or 1.0),
+        # GLM-4-MoE configurations do not spell these out; the family routes with sigmoid scores and a
+        # selection bias
+        scoring_func=getattr(hf, "scoring_func", "sigmoid"),
+        topk_method=getattr(hf, "topk_method", "noaux_tc"),
         swiglu_limit=getattr(hf, "swiglu_limit", None),
     )
 
