@@ -148,7 +148,8 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
 
 template <bool kGateUp, int N_MAX, bool kReturn = false>
 __global__ void __launch_bounds__(kReturn ? kThreadsWithReturn : kThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_args a) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_b,
+                    const mf_gemm_args a) {
   using Cfg = GemmCfg<kGateUp, N_MAX>;
   constexpr int STAGES = Cfg::kStages;
 
@@ -172,6 +173,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  // Token operand by TMA (contiguous rows) instead of the cp.async gather: warp 2 issues one bulk copy per
+  // stage, warp 3 has nothing to do.
+  const bool b_tma = a.b_tmap != nullptr;
   // Optional per-CTA time stamps: 0 entry, 1 dependencies met, 2 first weight tile requested, 3 first
   // operand stage complete, 4 first accumulator complete, 5 last epilogue done, 6 exit.
   unsigned long long* trace = a.trace ? a.trace + (size_t)blockIdx.x * 8 : nullptr;
@@ -179,7 +183,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1 + kGatherThreads);  // TMA expect_tx arrive + one per gather thread
+      // weight TMA expect_tx arrive + (one per gather thread | the token TMA expect_tx arrive)
+      mbar_init(&full_bar[s], b_tma ? 2 : 1 + kGatherThreads);
       mbar_init(&empty_bar[s], 1);                  // tcgen05.commit
     }
     for (int s = 0; s < kAccStages; ++s) {
@@ -193,6 +198,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
+    if (b_tma) tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -311,8 +317,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_ar
       __syncwarp();
       acc.advance(kAccStages);
     }
+  } else if (warp < 4 && b_tma) {
+    // ------------------------------------------------------------------ token-operand producer (TMA)
+    if (warp == 2) {
+      PipeState st;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const int ks = u % split;
+        const int tt = u / (split * a.m_blocks);
+        const int row_start = a.tile_s[tt];
+        for (int j = 0; j < kb_per; ++j) {
+          const int kb = ks * kb_per + j;
+          ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 2, blockIdx.x, 0);
+            break;
+          }
+          if (lane == 0) {
+            // the box is N_MAX rows whatever the tile's row count: rows past the tile (the next expert's
+            // entries, or zero fill past the end of the buffer) land in smem rows the MMA does not read
+            // or in accumulator columns the epilogue skips
+            mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageB);
+            tma_load_2d(sB + st.stage * Cfg::kStageB, &tmap_b, &full_bar[st.stage], kb * 64, row_start);
+          }
+          __syncwarp();
+          st.advance(STAGES);
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 100000ull) __nanosleep(1000);
+      }
+    }
   } else if (warp < 4) {
-    // ------------------------------------------------------------------ token-operand producers
+    // ------------------------------------------------------------------ token-operand producers (gather)
     const int gt = tid - 64;       // 0..63
     const int r_in = gt >> 3;      // row inside an 8-row group == swizzle phase
     const int chunk = gt & 7;      // 16-byte chunk inside the 128-byte row
@@ -556,10 +595,11 @@ static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStre
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  CUtensorMap tm;
+  CUtensorMap tm, tb;
   memcpy(&tm, tmap, sizeof(tm));
+  memcpy(&tb, args->b_tmap ? args->b_tmap : tmap, sizeof(tb));
   const int threads = kReturn ? kThreadsWithReturn : kThreads;
-  return (int)launch_kernel(kern, dim3(grid), dim3(threads), Cfg::kSmemBytes, stream, true, tm, *args);
+  return (int)launch_kernel(kern, dim3(grid), dim3(threads), Cfg::kSmemBytes, stream, true, tm, tb, *args);
 }
 
 static int check_args(const mf_gemm_args* a, int n_max, int grid) {
@@ -567,6 +607,7 @@ static int check_args(const mf_gemm_args* a, int n_max, int grid) {
   if (n_max != 32 && n_max != 64 && n_max != 128) return -2;
   if (a->m_blocks < 1 || a->k_blocks < 1) return -3;
   if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
+  if (a->b_tmap != nullptr && a->b_index != nullptr) return -5;  // TMA token tiles need contiguous rows
   return 0;
 }
 
@@ -574,21 +615,27 @@ static int check_args(const mf_gemm_args* a, int n_max, int grid) {
 
 extern "C" {
 
-int mf_make_weight_tmap(void* out_tmap, const void* w, long long rows, long long k_elems, int elem_bytes) {
+int mf_make_tile_tmap(void* out_tmap, const void* base, long long rows, long long k_elems, int elem_bytes,
+                      int box_rows) {
   auto fn = mf::get_encode_fn();
   if (!fn) return -10;
-  if ((reinterpret_cast<uintptr_t>(w) & 15) != 0 || ((k_elems * elem_bytes) & 15) != 0) return -11;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((k_elems * elem_bytes) & 15) != 0) return -11;
+  if (box_rows < 1 || box_rows > 256 || rows < 1) return -13;
   CUtensorMap tm;
   cuuint64_t dims[2] = {(cuuint64_t)k_elems, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)(k_elems * elem_bytes)};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 128};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  CUresult r = fn(&tm, dt, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(&tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -12 - (int)r * 100;
   memcpy(out_tmap, &tm, sizeof(tm));
   return 0;
+}
+
+int mf_make_weight_tmap(void* out_tmap, const void* w, long long rows, long long k_elems, int elem_bytes) {
+  return mf_make_tile_tmap(out_tmap, w, rows, k_elems, elem_bytes, 128);
 }
 
 int mf_gemm_smem_bytes(int gate_up, int n_max) {
@@ -688,9 +735,10 @@ extern "C" int mf_gemm_down_static_scratch(const void* tmap, const mf_gemm_args*
   a.partial = reinterpret_cast<float*>(base);
   a.counters = reinterpret_cast<int*>(base + kStaticPartialBytes);
   a.max_split_slots = MF_STATIC_SCRATCH_MAX_SLOTS;
+  a.b_tmap = nullptr;  // this entry always gathers the token rows
   CUtensorMap tm;
   memcpy(&tm, tmap, sizeof(tm));
   grouped_gemm_kernel<false, kStaticNMax>
-      <<<grid, kThreads, GemmCfg<false, kStaticNMax>::kSmemBytes, s>>>(tm, a);
+      <<<grid, kThreads, GemmCfg<false, kStaticNMax>::kSmemBytes, s>>>(tm, tm, a);
   return (int)cudaGetLastError();
 }

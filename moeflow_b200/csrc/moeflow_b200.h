@@ -66,10 +66,18 @@ typedef struct {
   const int* entry_row;      // [entries] received row of every expert-major entry
   const int* inv;            // [rows * top_k] (row, slot) -> entry, -1 = none
   int ret_rank, ret_R, ret_C, ret_K;
+  // Optional: host pointer to a 128-byte tensor map over the token operand viewed as [rows, K] with a box of
+  // n_max rows x 128 bytes (mf_make_tile_tmap).  When set, b_index must be NULL (entry n reads row
+  // b_base + n * b_pitch): token tiles are then fetched by TMA, one bulk copy per pipeline stage, instead of
+  // being gathered 16 bytes at a time.  Rows past a tile's end are fetched too and ignored.
+  const void* b_tmap;
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
 // 128 rows with the 128-byte swizzle.  `out_tmap` receives 128 bytes.
+// General form of mf_make_weight_tmap: boxes of box_rows rows x 128 bytes, 128-byte swizzle.
+int mf_make_tile_tmap(void* out_tmap, const void* base, long long rows, long long k_elems, int elem_bytes,
+                      int box_rows);
 int mf_make_weight_tmap(void* out_tmap, const void* w, long long rows, long long k_elems, int elem_bytes);
 
 int mf_gemm_gate_up(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream);

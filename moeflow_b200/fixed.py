@@ -447,7 +447,7 @@ class FixedEPLayer:
         self.tile_s = torch.zeros(self.max_tiles, **i32)
         self.tile_n = torch.zeros(self.max_tiles, **i32)
         self.plan = torch.zeros(_lib.PLAN_WORDS, **i32)
-        self.act = torch.zeros(N, I, dtype=torch.bfloat16, device=dev)
+        self.act = torch.zeros(max(N, self.block_m), I, dtype=torch.bfloat16, device=dev)  # >= one TMA box of rows
         self.y = torch.zeros(N, H, dtype=torch.bfloat16, device=dev)
         mb1, mb2 = I // 128, H // 128
         self._counters1 = torch.zeros(self.max_tiles * mb1 * 4, **i32)
@@ -498,6 +498,14 @@ class FixedEPLayer:
             k_blocks=I // 64, rows_per_expert=H, up_row_offset=0, out=self.y.data_ptr(), out_pitch=H,
             row_scale=self.entry_w.data_ptr(), counters=self._counters2.data_ptr(), **common,
         )
+        # The down GEMM reads its token operand (act, contiguous in expert-major order) by TMA, one bulk copy
+        # per pipeline stage; gemm_kwargs b_tma=False falls back to the 16-byte gather the gate/up GEMM uses.
+        self._tmap_act = None
+        if bool(self.gemm_kwargs.get("b_tma", True)):
+            from .ops.kernels import make_tile_tmap
+
+            self._tmap_act = make_tile_tmap(self.act, self.block_m)
+            self._a_gemm2.b_tmap = C.addressof(self._tmap_act)
         # Owner reduce + return push can run inside the down GEMM (gemm_kwargs fuse_return=True: four extra
         # warps reduce a row as soon as its last slot is written and store it into the source rank's
         # buffer) or as the separate owner_reduce_push kernel chained by programmatic launch.  Measured on

@@ -69,6 +69,7 @@ class GemmArgs(C.Structure):
         ("ret_R", C.c_int),
         ("ret_C", C.c_int),
         ("ret_K", C.c_int),
+        ("b_tmap", C.c_void_p),
     ]
 
 
@@ -205,6 +206,7 @@ def lib() -> C.CDLL:
     P, I, LL, ULL, F = C.c_void_p, C.c_int, C.c_longlong, C.c_ulonglong, C.c_float
     sigs = {
         "mf_make_weight_tmap": [P, P, LL, LL, I],
+        "mf_make_tile_tmap": [P, P, LL, LL, I, I],
         "mf_gemm_gate_up": [P, C.POINTER(GemmArgs), I, I, P],
         "mf_gemm_down": [P, C.POINTER(GemmArgs), I, I, P],
         "mf_gemm_smem_bytes": [I, I],

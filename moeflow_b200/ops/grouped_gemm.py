@@ -19,7 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from .kernels import make_weight_tmap, sm_count
+from .kernels import make_tile_tmap, make_weight_tmap, sm_count
 
 
 @dataclass
@@ -113,8 +113,13 @@ def down_proj(
     status: torch.Tensor | None = None,
     wait_ns: int = 2_000_000_000,
     grid: int | None = None,
+    b_tma: bool = True,
 ) -> torch.Tensor:
-    """``y[n] = bf16(row_scale[n] * (act[n] . W2[e_n]^T))`` per expert segment."""
+    """``y[n] = bf16(row_scale[n] * (act[n] . W2[e_n]^T))`` per expert segment.
+
+    ``b_tma``: fetch the token tiles of ``act`` by TMA (its rows are contiguous); ``False`` gathers them
+    16 bytes at a time like the gate/up GEMM does for indexed rows.
+    """
     n_exp, hidden, inter = w2.shape
     if act.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16:
         raise ValueError("bf16 only")
@@ -135,6 +140,10 @@ def down_proj(
         row_scale=_lib.ptr(row_scale), partial=partial.data_ptr(), counters=counters.data_ptr(), max_split_slots=slots,
         limit=0.0, round_h=0, status=status.data_ptr(), wait_ns=wait_ns,
     )
+    tmap_b = None
+    if b_tma:
+        tmap_b = make_tile_tmap(act, tp.block_m)
+        args.b_tmap = C.addressof(tmap_b)
     grid = grid or sm_count(dev.index or 0)
     _lib.check(_lib.lib().mf_gemm_down(tmap, C.byref(args), tp.block_m, grid, _lib.stream_ptr()), "down gemm")
     y._keep = (w2, partial, counters, status, row_scale, act)

@@ -76,6 +76,21 @@ def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, out: torch.
     return out
 
 
+def make_tile_tmap(x: torch.Tensor, box_rows: int) -> C.Array:
+    """128-byte TMA descriptor over a contiguous ``x [rows, K]`` with boxes of ``box_rows`` rows x 128 bytes.
+
+    Used for the token operand of the down GEMM (its rows are contiguous in expert-major order), with
+    ``box_rows`` equal to the kernel's token-tile width.  The buffer must outlive every launch that uses it.
+    """
+    _need_cuda(x, "token operand")
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("the token operand must be a contiguous [rows, K] tensor")
+    buf = (C.c_ubyte * 128)()
+    _lib.check(_lib.lib().mf_make_tile_tmap(buf, x.data_ptr(), x.shape[0], x.shape[1], x.element_size(), box_rows),
+               "tensor map")
+    return buf
+
+
 def make_weight_tmap(w: torch.Tensor) -> C.Array:
     """128-byte TMA descriptor over ``w`` viewed as ``[rows, K]`` (K innermost, 128 B x 128 row boxes)."""
     _need_cuda(w, "weight")

@@ -151,3 +151,22 @@ def test_expert_compute_backend_matches_the_torch_loop(weighted):
     torch.cuda.synchronize()
     assert got.shape == a.shape and got.dtype == a.dtype
     assert normwise_rel_err(got, ref) < 6 * 2.0**-8, normwise_rel_err(got, ref)
+
+
+@pytest.mark.parametrize("counts,block_m,split", [([3, 0, 17, 5], 64, 1), ([70, 2, 130], 64, 2), ([100, 20], 128, 1), ([5, 9], 32, 4)])
+def test_down_proj_token_tiles_by_tma_equal_the_gather_bitwise(counts, block_m, split):
+    """The token operand of the down GEMM fetched by TMA (box of block_m rows) or gathered by cp.async."""
+    from moeflow_b200.ops.grouped_gemm import down_proj, plan_from_offsets
+
+    _, w2, _, _, offsets, scale = _problem(counts, 512, 256, seed=21)
+    n = offsets[-1]
+    g = torch.Generator().manual_seed(3)
+    act = torch.randn(n, 256, generator=g).bfloat16().cuda()
+    tp = plan_from_offsets(offsets, block_m, act.device)
+    status = torch.zeros(1, dtype=torch.int64, device=act.device)
+    a = down_proj(act, w2, tp, row_scale=scale[:n], split=split, status=status, wait_ns=50_000_000, b_tma=True).clone()
+    b = down_proj(act, w2, tp, row_scale=scale[:n], split=split, status=status, wait_ns=50_000_000, b_tma=False).clone()
+    torch.cuda.synchronize()
+    _status_ok(status)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert normwise_rel_err(a, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8
