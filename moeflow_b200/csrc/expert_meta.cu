@@ -241,6 +241,217 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Multi-CTA variant for prefill sizes: the flat (row, slot) index space is cut into one contiguous
+// chunk per CTA (and inside a CTA into one contiguous range per warp, as above).  Launch 1 counts:
+// per-CTA expert histograms go to cta_hist.  Launch 2 recomputes its own per-warp histograms, adds the
+// counts of the CTAs before it (a plain loop over cta_hist: no atomics, no waiting between CTAs, so the
+// layout is again the same on every run and equal to the single-CTA kernel's) and places its entries.
+// ---------------------------------------------------------------------------------------------------
+struct MetaRange {
+  int begin, end;
+};
+__device__ __forceinline__ MetaRange meta_range(int N, int n_ctas, int cta, int warp) {
+  int chunk = (N + n_ctas - 1) / n_ctas;
+  chunk = (chunk + 31) & ~31;
+  const int cb = min(N, cta * chunk), ce = min(N, (cta + 1) * chunk);
+  int per = (ce - cb + kMetaWarps - 1) / kMetaWarps;
+  per = (per + 31) & ~31;
+  MetaRange r;
+  r.begin = min(ce, cb + warp * per);
+  r.end = min(ce, cb + (warp + 1) * per);
+  return r;
+}
+
+// keys (local expert id or -1) and weight bits of kMetaBatch warp-wide steps starting at i0
+__device__ __forceinline__ void meta_load_keys(const mf_meta_args& a, int i0, int end, int lane, bool want_w,
+                                               int (&key)[kMetaBatch], int (&wbits)[kMetaBatch]) {
+  const uint8_t* recv = static_cast<const uint8_t*>(a.recv);
+  const size_t meta_off = (size_t)a.H * 2;
+#pragma unroll
+  for (int b = 0; b < kMetaBatch; ++b) {
+    const int i = i0 + b * 32 + lane;
+    key[b] = -1;
+    wbits[b] = 0;
+    if (i < end) {
+      const int row = i / a.K, slot = i - row * a.K;
+      const int* meta = reinterpret_cast<const int*>(recv + (size_t)row * a.pitch + meta_off);
+      const int id = meta[slot];
+      const int valid = meta[2 * a.K];
+      const int wb = want_w ? meta[a.K + slot] : 0;
+      if (valid != 0 && id >= 0 && id < a.L) {
+        key[b] = id;
+        wbits[b] = wb;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void meta_histogram(const mf_meta_args& a, MetaRange r, int lane, int* my_hist) {
+  for (int i0 = r.begin; i0 < r.end; i0 += 32 * kMetaBatch) {
+    int key[kMetaBatch], wbits[kMetaBatch];
+    meta_load_keys(a, i0, r.end, lane, false, key, wbits);
+#pragma unroll
+    for (int b = 0; b < kMetaBatch; ++b) {
+      const unsigned same = __match_any_sync(0xffffffffu, key[b]);
+      if (key[b] >= 0 && lane == __ffs(same) - 1) my_hist[key[b]] += __popc(same);
+      __syncwarp();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMetaThreads) expert_meta_count_kernel(const mf_meta_args a) {
+  extern __shared__ int sm[];
+  const int L = a.L, K = a.K;
+  int* hist = sm;                    // [kMetaWarps][L]
+  int* warp_sums = hist + kMetaWarps * L;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cta = blockIdx.x, n_ctas = gridDim.x;
+  grid_dep_launch();
+  for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
+  if (tid == 0) warp_sums[0] = 0;
+  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
+  const unsigned epoch = a.epoch ? *a.epoch : 0u;
+  if (a.flags != nullptr && tid < a.R) {
+    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kDispatchFlagTimeout, tid, cta, epoch);
+  }
+  for (int i = cta * kMetaThreads + tid; i < a.n_counters1; i += n_ctas * kMetaThreads) a.counters1[i] = 0;
+  for (int i = cta * kMetaThreads + tid; i < a.n_counters2; i += n_ctas * kMetaThreads) a.counters2[i] = 0;
+  __syncthreads();
+
+  const int N = a.rows * K;
+  meta_histogram(a, meta_range(N, n_ctas, cta, warp), lane, hist + warp * L);
+  __syncthreads();
+  for (int e = tid; e < L; e += kMetaThreads) {
+    int total = 0;
+    for (int w = 0; w < kMetaWarps; ++w) total += hist[w * L + e];
+    a.cta_hist[(size_t)cta * L + e] = total;
+  }
+  // slots per received row, and the number of rows with at least one
+  const uint8_t* recv = static_cast<const uint8_t*>(a.recv);
+  const size_t meta_off = (size_t)a.H * 2;
+  int mine = 0;
+  for (int r = cta * kMetaThreads + tid; r < a.rows; r += n_ctas * kMetaThreads) {
+    const int* meta = reinterpret_cast<const int*>(recv + (size_t)r * a.pitch + meta_off);
+    int hits = 0;
+    if (meta[2 * K] != 0)
+      for (int k = 0; k < K; ++k) hits += (meta[k] >= 0 && meta[k] < L) ? 1 : 0;
+    if (a.row_hits != nullptr) a.row_hits[r] = hits;
+    mine += hits > 0 ? 1 : 0;
+  }
+  if (mine) atomicAdd(&warp_sums[0], mine);
+  __syncthreads();
+  if (tid == 0 && warp_sums[0] != 0) atomicAdd(&a.acc[0], warp_sums[0]);  // a count: the order does not matter
+}
+
+__global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const mf_meta_args a) {
+  extern __shared__ int sm[];
+  const int L = a.L, K = a.K;
+  int* hist = sm;                       // [kMetaWarps][L]
+  int* cnt = hist + kMetaWarps * L;     // [L] entries of the expert over all CTAs
+  int* offs = cnt + L;                  // [L] first position of this CTA's entries of the expert
+  int* warp_sums = offs + L;            // [40]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cta = blockIdx.x, n_ctas = gridDim.x;
+  grid_dep_launch();
+  for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
+  if (tid == 0) warp_sums[34] = 0;
+  grid_dep_wait();  // the count launch has completed (and with it the dispatch kernel)
+  __syncthreads();
+
+  const int N = a.rows * K;
+  const MetaRange range = meta_range(N, n_ctas, cta, warp);
+  int* my_hist = hist + warp * L;
+  meta_histogram(a, range, lane, my_hist);
+  __syncthreads();
+
+  for (int e = tid; e < L; e += kMetaThreads) {
+    int run = 0;
+    for (int w = 0; w < kMetaWarps; ++w) {
+      const int c = hist[w * L + e];
+      hist[w * L + e] = run;
+      run += c;
+    }
+    int before = 0, total = 0;
+    for (int c = 0; c < n_ctas; ++c) {
+      const int v = a.cta_hist[(size_t)c * L + e];
+      before += c < cta ? v : 0;
+      total += v;
+    }
+    cnt[e] = total;
+    offs[e] = before;
+  }
+  __syncthreads();
+
+  const int my_cnt = tid < L ? cnt[tid] : 0;
+  int n_entries, n_tiles;
+  const int my_off = block_exclusive_scan(my_cnt, warp_sums, n_entries);
+  const int my_nt = (my_cnt + a.block_m - 1) / a.block_m;
+  const int my_tb = block_exclusive_scan(my_nt, warp_sums, n_tiles);
+  if (tid < L) {
+    offs[tid] += my_off;
+    if (cta == 0) {
+      a.offsets[tid] = my_off;
+      for (int j = 0; j < my_nt; ++j) {
+        const int idx = my_tb + j;
+        if (idx < a.max_tiles) {
+          a.tile_e[idx] = tid;
+          a.tile_s[idx] = my_off + j * a.block_m;
+          a.tile_n[idx] = min(a.block_m, my_cnt - j * a.block_m);
+        }
+      }
+      if (my_cnt > 0) atomicMax(&warp_sums[34], min(my_cnt, a.block_m));
+    }
+  }
+  __syncthreads();
+  if (cta == 0 && tid == 0) {
+    a.offsets[L] = n_entries;
+    const int nt = min(n_tiles, a.max_tiles);
+    int cols = (warp_sums[34] + 15) & ~15;
+    if (cols < 16) cols = 16;
+    int slots1 = a.max_split_slots, slots2 = a.max_split_slots;
+    if (a.partial_floats > 0) {
+      slots1 = (int)min((long long)0x7fffffff, a.partial_floats / (2ll * cols * 128));
+      slots2 = (int)min((long long)0x7fffffff, a.partial_floats / (1ll * cols * 128));
+    } else {
+      cols = 0;
+    }
+    a.plan[MF_PLAN_N_TILES] = nt;
+    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4);
+    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8);
+    a.plan[MF_PLAN_N_ENTRIES] = n_entries;
+    a.plan[MF_PLAN_SLOT_COLS] = cols;
+    a.plan[MF_PLAN_VALID_ROWS] = a.acc[0];
+    a.acc[0] = 0;  // ready for the next forward (its count launch runs after this one)
+  }
+
+  for (int i0 = range.begin; i0 < range.end; i0 += 32 * kMetaBatch) {
+    int key[kMetaBatch], wbits[kMetaBatch];
+    meta_load_keys(a, i0, range.end, lane, true, key, wbits);
+#pragma unroll
+    for (int b = 0; b < kMetaBatch; ++b) {
+      const int i = i0 + b * 32 + lane;
+      const unsigned same = __match_any_sync(0xffffffffu, key[b]);
+      if (key[b] >= 0) {
+        const int pos = offs[key[b]] + my_hist[key[b]] + __popc(same & ((1u << lane) - 1u));
+        if (pos < N) {
+          const int row = i / K;
+          a.entry_row[pos] = row;
+          a.entry_slot[pos] = i - row * K;
+          a.entry_w[pos] = __int_as_float(wbits[b]);
+        }
+        a.inv[i] = pos < N ? pos : -1;
+      } else if (i < range.end) {
+        a.inv[i] = -1;
+      }
+      __syncwarp();
+      if (key[b] >= 0 && lane == __ffs(same) - 1) my_hist[key[b]] += __popc(same);
+      __syncwarp();
+    }
+  }
+}
+
 }  // namespace mf
 
 extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
@@ -250,9 +461,21 @@ extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
   if (smem > 48 * 1024 && smem > configured) {
     cudaError_t e =
         cudaFuncSetAttribute(mf::expert_meta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(mf::expert_meta_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(mf::expert_meta_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  return (int)mf::launch_kernel(mf::expert_meta_kernel, dim3(1), dim3(mf::kMetaThreads), smem,
-                                static_cast<cudaStream_t>(stream), true, *a);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a->n_ctas > 1) {
+    if (!a->cta_hist || !a->acc || a->n_ctas > 1024) return -2;
+    cudaError_t e = mf::launch_kernel(mf::expert_meta_count_kernel, dim3(a->n_ctas), dim3(mf::kMetaThreads), smem, s,
+                                      true, *a);
+    if (e != cudaSuccess) return (int)e;
+    return (int)mf::launch_kernel(mf::expert_meta_place_kernel, dim3(a->n_ctas), dim3(mf::kMetaThreads), smem, s, true,
+                                  *a);
+  }
+  return (int)mf::launch_kernel(mf::expert_meta_kernel, dim3(1), dim3(mf::kMetaThreads), smem, s, true, *a);
 }

@@ -177,6 +177,12 @@ typedef struct {
   unsigned long long wait_ns;
   long long partial_floats;  // capacity of the split-K scratch in floats: bounds slots = floats / (tiles * cols * 128)
   int* row_hits;             // optional [rows]: valid slots per received row (for the fused return path)
+  // Multi-CTA variant (prefill sizes): with n_ctas > 1 the work is split over n_ctas CTAs in two chained
+  // launches (count, then scan + place); cta_hist [n_ctas * L] and acc [2] are its scratch (acc zeroed once
+  // by the caller, left zero by every call).  Results are identical to the single-CTA kernel.
+  int n_ctas;
+  int* cta_hist;
+  int* acc;
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 

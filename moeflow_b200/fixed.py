@@ -481,6 +481,21 @@ class FixedEPLayer:
             max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
             partial_floats=partial_floats,
         )
+        # Metadata: one CTA for decode sizes; for prefill sizes (many received rows) the counting sort is
+        # split over several CTAs in two chained launches.  Same result either way.
+        n_words = R * Cc * K
+        # measured on B200: the single CTA takes 10 / 14 / 20 / 32 / 134 us at 1024 / 2048 / 4096 / 8192 / 32768
+        # slot words, the two chained multi-CTA launches 11-18 us throughout
+        auto_ctas = 1 if n_words < 2048 else min(self.n_sms, (n_words + 127) // 128)
+        self.meta_ctas = int(self.gemm_kwargs.get("meta_ctas", auto_ctas))
+        if not 1 <= self.meta_ctas <= 1024:
+            raise ValueError("meta_ctas must be between 1 and 1024")
+        if self.meta_ctas > 1:
+            self._cta_hist = torch.zeros(self.meta_ctas * L, **i32)
+            self._meta_acc = torch.zeros(2, **i32)
+            self._a_meta.n_ctas = self.meta_ctas
+            self._a_meta.cta_hist = self._cta_hist.data_ptr()
+            self._a_meta.acc = self._meta_acc.data_ptr()
         limit = cfg.swiglu_limit if cfg.swiglu_limit is not None else 0.0
         common = dict(
             tile_e=self.tile_e.data_ptr(), tile_s=self.tile_s.data_ptr(), tile_n=self.tile_n.data_ptr(),

@@ -24,7 +24,9 @@ class GraphedMoELayer:
         self.num_valid = torch.full((), layer.C, dtype=torch.int32, device=dev)
         self.graph: torch.cuda.CUDAGraph | None = None
         self._warmup = warmup
-        self.kernels_per_step = 5 if getattr(layer, "fuse_return", False) else 6  # route+dispatch, meta, gate/up, down(+reduce+push), combine
+        # route+dispatch, meta (two launches in its multi-CTA form), gate/up, down(+reduce+push), combine
+        self.kernels_per_step = (5 if getattr(layer, "fuse_return", False) else 6) + (
+            1 if getattr(layer, "meta_ctas", 1) > 1 else 0)
 
     def _forward(self) -> torch.Tensor:
         return self.layer.forward(self.x, self.logits, self.bias, self.num_valid)

@@ -142,6 +142,9 @@ class MetaArgs(C.Structure):
         ("wait_ns", C.c_ulonglong),
         ("partial_floats", C.c_longlong),
         ("row_hits", C.c_void_p),
+        ("n_ctas", C.c_int),
+        ("cta_hist", C.c_void_p),
+        ("acc", C.c_void_p),
     ]
 
 

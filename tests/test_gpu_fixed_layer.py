@@ -72,13 +72,15 @@ def test_dispatch_rows_bitwise_equal_torch_twin(world, dist):
                                      tw[r].recv[s, :t, : cfg.hidden_size].contiguous())
 
 
+@pytest.mark.parametrize("meta_ctas", [1, 3, 7])
 @pytest.mark.parametrize("world,cap", [(1, 8), (2, 16), (4, 32)])
-def test_expert_meta_matches_torch_layout(world, cap):
+def test_expert_meta_matches_torch_layout(world, cap, meta_ctas):
+    """Single-CTA kernel and the multi-CTA count + place pair against the torch layout."""
     cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4)
     w13, w2 = make_weights(cfg, 0, device="cuda")
     tokens = [cap, cap // 2, 1, 0][:world]
     xs, lgs = _inputs(cfg, world, tokens, 3)
-    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    cu = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"meta_ctas": meta_ctas})
     for ly, x, lg in zip(cu, xs, lgs):
         ly.stage_pack(x, lg, None)
     for ly in cu:
@@ -100,6 +102,39 @@ def test_expert_meta_matches_torch_layout(world, cap):
         got = list(zip(ly.tile_e[: plan[0]].tolist(), ly.tile_s[: plan[0]].tolist(), ly.tile_n[: plan[0]].tolist()))
         assert got == tiles
         assert plan[1] in (1, 2, 4, 8) and plan[2] in (1, 2, 4, 8)
+        live_rows = int((local >= 0).any(dim=-1).sum())
+        assert plan[5] == live_rows  # rows with at least one local slot
+
+
+def test_multi_cta_metadata_equals_the_single_cta_kernel_at_prefill_size():
+    """2048 tokens on one rank (16384 slot words): every output array and the plan are identical, and a
+    second forward (the scratch counter must have been left at zero) is identical again."""
+    cfg = replace(SMALL_GPU, n_routed_experts=32, top_k=8)
+    cap = 2048
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    xs, lgs = _inputs(cfg, 1, [cap - 37], 11)
+    one = _layers(cfg, 1, cap, w13, w2, "cuda", gemm_kwargs={"meta_ctas": 1})[0]
+    many = _layers(cfg, 1, cap, w13, w2, "cuda")[0]
+    assert many.meta_ctas > 1 and one.meta_ctas == 1
+    for rep in range(2):
+        for ly in (one, many):
+            ly.stage_pack(xs[0], lgs[0], None)
+            ly._cuda_meta()
+        torch.cuda.synchronize()
+        _ok(one), _ok(many)
+        n = int(one.offsets[-1])
+        assert n > 0 and torch.equal(one.offsets, many.offsets) and torch.equal(one.plan, many.plan)
+        for name in ("entry_row", "entry_slot", "entry_w"):
+            assert torch.equal(getattr(one, name)[:n], getattr(many, name)[:n]), name
+        assert torch.equal(one.inv, many.inv) and torch.equal(one.row_hits, many.row_hits)
+        nt = int(one.plan[0])
+        for name in ("tile_e", "tile_s", "tile_n"):
+            assert torch.equal(getattr(one, name)[:nt], getattr(many, name)[:nt]), name
+    out_one = one.forward(xs[0], lgs[0], None).clone()
+    out_many = many.forward(xs[0], lgs[0], None).clone()
+    torch.cuda.synchronize()
+    _ok(many)
+    assert bitwise_equal(out_one, out_many)
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
