@@ -57,15 +57,19 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& 
 // Pick the K split S in {1,2,4,8}.  Cost model in units of one K block of streaming: a unit costs its
 // K blocks plus a fixed overhead (pipeline fill, epilogue, and for S > 1 the partial-sum round trip);
 // the kernel takes ceil(units * S / SMs) rounds of such units.  Ties go to the smaller S.
-__device__ __forceinline__ int choose_split(int units, int k_blocks, int n_sms, int max_slots, int overhead_kb) {
+__device__ __forceinline__ int choose_split(int units, int k_blocks, int n_sms, int max_slots, int overhead_kb,
+                                            int cols) {
   if (units <= 0) return 1;
   int best = 1;
   long long best_cost = (long long)((units + n_sms - 1) / n_sms) * (k_blocks + overhead_kb);
+  // the partial-sum round trip of a split unit grows with the tile's token columns (measured: splitting
+  // 64-column tiles in two cost more than the idle SMs of an uneven last round)
+  const int wide = cols > 16 ? (cols - 16) / 8 : 0;
   for (int s = 2; s <= 8; s <<= 1) {
     if (k_blocks % s != 0 || k_blocks / s < 2) break;
     if ((long long)units * s > max_slots) break;
     const long long rounds = ((long long)units * s + n_sms - 1) / n_sms;
-    const long long cost = rounds * (k_blocks / s + overhead_kb + 1);
+    const long long cost = rounds * (k_blocks / s + overhead_kb + 1 + wide);
     if (cost < best_cost) {
       best_cost = cost;
       best = s;
@@ -196,6 +200,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
     const int nt = min(n_tiles, a.max_tiles);
     int cols = (warp_sums[34] + 15) & ~15;
     if (cols < 16) cols = 16;
+    const int wide_cols = cols;
     int slots1 = a.max_split_slots, slots2 = a.max_split_slots;
     if (a.partial_floats > 0) {
       slots1 = (int)min((long long)0x7fffffff, a.partial_floats / (2ll * cols * 128));
@@ -204,8 +209,8 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
       cols = 0;  // fixed slots of the kernel's n_max columns
     }
     a.plan[MF_PLAN_N_TILES] = nt;
-    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4);
-    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8);
+    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4, wide_cols);
+    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8, wide_cols);
     a.plan[MF_PLAN_N_ENTRIES] = n_entries;
     a.plan[MF_PLAN_SLOT_COLS] = cols;
     a.plan[MF_PLAN_VALID_ROWS] = warp_sums[35];
@@ -410,6 +415,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const m
     const int nt = min(n_tiles, a.max_tiles);
     int cols = (warp_sums[34] + 15) & ~15;
     if (cols < 16) cols = 16;
+    const int wide_cols = cols;
     int slots1 = a.max_split_slots, slots2 = a.max_split_slots;
     if (a.partial_floats > 0) {
       slots1 = (int)min((long long)0x7fffffff, a.partial_floats / (2ll * cols * 128));
@@ -418,8 +424,8 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const m
       cols = 0;
     }
     a.plan[MF_PLAN_N_TILES] = nt;
-    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4);
-    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8);
+    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4, wide_cols);
+    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8, wide_cols);
     a.plan[MF_PLAN_N_ENTRIES] = n_entries;
     a.plan[MF_PLAN_SLOT_COLS] = cols;
     a.plan[MF_PLAN_VALID_ROWS] = a.acc[0];
