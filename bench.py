@@ -338,7 +338,7 @@ def main() -> None:
     ROUTING = args.dist
 
     if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "moeflow" / "fixed.py").exists():
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of /root/reference)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip --target install of the reference checkout)"}))
         return
     rank, world, dev = init_dist(args.gpus)
     if args.impl == "reference":
