@@ -57,8 +57,8 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& 
 // Pick the K split S in {1,2,4,8}.  Cost model in units of one K block of streaming: a unit costs its
 // K blocks plus a fixed overhead (pipeline fill, epilogue, and for S > 1 the partial-sum round trip);
 // the kernel takes ceil(units * S / SMs) rounds of such units.  Ties go to the smaller S.
-__device__ __forceinline__ int choose_split(int units, int k_blocks, int n_sms, int max_slots, int overhead_kb,
-                                            int cols) {
+__host__ __device__ __forceinline__ int choose_split(int units, int k_blocks, int n_sms, int max_slots,
+                                                     int overhead_kb, int cols) {
   if (units <= 0) return 1;
   int best = 1;
   long long best_cost = (long long)((units + n_sms - 1) / n_sms) * (k_blocks + overhead_kb);
@@ -459,6 +459,10 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const m
 }
 
 }  // namespace mf
+
+extern "C" int mf_plan_split(int units, int k_blocks, int n_sms, int max_slots, int overhead_kb, int cols) {
+  return mf::choose_split(units, k_blocks, n_sms, max_slots, overhead_kb, cols);
+}
 
 extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
   if (!a || a->L < 1 || a->L > mf::kMetaThreads || a->R > mf::kMetaThreads || a->block_m < 1) return -1;

@@ -185,6 +185,11 @@ typedef struct {
   int* acc;
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
+// The K-split rule of the metadata kernels, callable on the host (no device needed): the split in {1,2,4,8}
+// for `units` (token tile, 128-row block) work items of `k_blocks` K blocks on `n_sms` persistent CTAs, given
+// `max_slots` partial-sum slots, the fixed per-unit overhead in K-block units (4 for gate/up, 8 for down) and
+// the tile's token columns `cols`.
+int mf_plan_split(int units, int k_blocks, int n_sms, int max_slots, int overhead_kb, int cols);
 
 // ---- owner reduce + return push, combine -------------------------------------------------------------
 typedef struct {

@@ -424,8 +424,7 @@ class FixedEPLayer:
         # number of times an expert's weights are streamed.  The estimate is the expectation under even
         # routing (R*C*K entries over R*L experts), not the worst case: wide tiles cost pipeline stages, and
         # with few rows per expert the narrower tile keeps more weight bytes in flight.
-        rows_per_expert = (Cc * K) / max(L, 1)
-        self.block_m = int(self.gemm_kwargs.get("block_m", 128 if rows_per_expert >= 96 else 64))
+        self.block_m = int(self.gemm_kwargs.get("block_m", choose_block_m(Cc, K, L)))
         if self.block_m not in (32, 64, 128):
             raise ValueError("block_m must be 32, 64 or 128")
         self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
@@ -486,8 +485,7 @@ class FixedEPLayer:
         n_words = R * Cc * K
         # measured on B200: the single CTA takes 10 / 14 / 20 / 32 / 134 us at 1024 / 2048 / 4096 / 8192 / 32768
         # slot words, the two chained multi-CTA launches 11-18 us throughout
-        auto_ctas = 1 if n_words < 2048 else min(self.n_sms, (n_words + 127) // 128)
-        self.meta_ctas = int(self.gemm_kwargs.get("meta_ctas", auto_ctas))
+        self.meta_ctas = int(self.gemm_kwargs.get("meta_ctas", choose_meta_ctas(n_words, self.n_sms)))
         if not 1 <= self.meta_ctas <= 1024:
             raise ValueError("meta_ctas must be between 1 and 1024")
         if self.meta_ctas > 1:
@@ -747,6 +745,20 @@ class _CudaLayout:
         self.dflag_off = self.ret_off + up(world * capacity * cfg.hidden_size * 2)
         self.rflag_off = self.dflag_off + up(world * 4, 256)
         self.total = self.rflag_off + up(world * 4, 256)
+
+
+def choose_block_m(capacity: int, top_k: int, local_experts: int) -> int:
+    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up (prefill).
+
+    The expectation is the one under even routing: ``R * C * K`` entries over ``R * L`` experts.
+    """
+    return 128 if (capacity * top_k) / max(local_experts, 1) >= 96 else 64
+
+
+def choose_meta_ctas(slot_words: int, n_sms: int) -> int:
+    """CTAs of the metadata pass for ``rows * K`` received slot words: one below 2048, else one per 128 words
+    up to one per SM."""
+    return 1 if slot_words < 2048 else max(2, min(n_sms, (slot_words + 127) // 128))
 
 
 def _cuda_ok(cfg: MoEConfig) -> bool:
