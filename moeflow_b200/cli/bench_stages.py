@@ -49,6 +49,8 @@ def main() -> None:
     ap.add_argument("--only-full", action="store_true", help="time only the whole layer (profiling runs)")
     ap.add_argument("--block-m", type=int, default=None, help="token rows per GEMM tile (32, 64, 128); default: chosen by the layer")
     ap.add_argument("--meta-ctas", type=int, default=None, help="CTAs of the metadata pass (1 = single-CTA kernel); default: by size")
+    ap.add_argument("--permute-rows", action="store_true",
+                    help="copy received rows into expert-major order so the gate/up GEMM reads token tiles by TMA")
     ap.add_argument("--fuse-return", type=int, default=None, help="1/0: owner reduce + return push inside the down GEMM or as its own kernel")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights (quantised from the bf16 ones)")
     ap.add_argument("--out", default=None)
@@ -85,6 +87,7 @@ def main() -> None:
                              gemm_kwargs={**({"block_m": 64} if args.fp8 else {}),
                                           **({"block_m": args.block_m} if args.block_m else {}),
                                           **({"meta_ctas": args.meta_ctas} if args.meta_ctas else {}),
+                                          **({"permute_rows": True} if args.permute_rows else {}),
                                           **({"fuse_return": bool(args.fuse_return)} if args.fuse_return is not None else {})})
         if args.fp8:
             layer.set_weights_fp8(*fp8_pack)

@@ -225,6 +225,11 @@ int mf_combine(const mf_combine_args* args, mf_stream_t stream);
 int mf_expert_prepare(const void* rows, long long pitch, int n_rows, int H, int K, int rank_offset, int filler,
                       void* hidden, int* ids32, long long* ids64, float* weights, mf_stream_t stream);
 
+// Expert-major copy of the received hidden rows: xg[pos, :H] = recv row entry_row[pos] for pos < plan[N_ENTRIES]
+// (so that the gate/up GEMM can read token tiles by TMA; see mf_gemm_args.b_tmap).  `grid` CTAs loop over the entries.
+int mf_permute_rows(const void* recv, long long pitch, const int* entry_row, const int* plan, void* xg, int H,
+                    int n_rows, int grid, mf_stream_t stream);
+
 // ---- activation quantisation (1x128 groups -> e4m3 + fp32 scales) --------------------------------------
 // q[r, :] = e4m3(x[src(r), :] / scale), scales[r, g] = max(amax_g, 1e-10) / 448 for every 128-wide group g.
 // src(r) = row_index ? row_index[r] : r.  With valid_off >= 0 a source row whose int32 at that byte offset is

@@ -205,3 +205,37 @@ extern "C" int mf_expert_prepare(const void* rows, long long pitch, int n_rows, 
                                 static_cast<cudaStream_t>(stream), true, static_cast<const uint8_t*>(rows), pitch, H, K,
                                 rank_offset, filler, static_cast<uint4*>(hidden), ids32, ids64, weights);
 }
+
+// -------------------------------------------------------------------------------------------------
+// Expert-major copy of the received hidden rows: xg[pos] = hidden lanes of received row entry_row[pos]
+// for every expert-major position pos < n_entries (plan word).  With it the gate/up GEMM can fetch its
+// token tiles by TMA like the down GEMM does (prefill sizes, where the 16-byte gather is the limiter);
+// the copy costs one extra read and write of the gathered rows.  No counterpart in the reference, whose
+// Triton GEMM gathers through its row index.
+// -------------------------------------------------------------------------------------------------
+namespace mf {
+__global__ void __launch_bounds__(kRowThreads)
+permute_rows_kernel(const uint8_t* __restrict__ recv, long long pitch, const int* __restrict__ entry_row,
+                    const int* __restrict__ plan, uint4* __restrict__ xg, int H, int n_rows) {
+  grid_dep_launch();
+  grid_dep_wait();  // the metadata pass has completed: entry_row and the plan are final
+  const int n_entries = plan[MF_PLAN_N_ENTRIES];
+  const int chunks = H / 8;
+  for (int pos = blockIdx.x; pos < n_entries; pos += gridDim.x) {
+    const int r = entry_row[pos];
+    if (r < 0 || r >= n_rows) continue;  // never taken for a consistent layout; keeps a bad index from being followed
+    const uint4* src = reinterpret_cast<const uint4*>(recv + (size_t)r * pitch);
+    uint4* dst = xg + (size_t)pos * chunks;
+    for (int c = threadIdx.x; c < chunks; c += kRowThreads) dst[c] = src[c];
+  }
+}
+}  // namespace mf
+
+extern "C" int mf_permute_rows(const void* recv, long long pitch, const int* entry_row, const int* plan, void* xg, int H,
+                               int n_rows, int grid, mf_stream_t stream) {
+  if (!recv || !entry_row || !plan || !xg || H % 8 != 0 || (pitch & 15) != 0 || grid < 1 || n_rows < 1) return -1;
+  return (int)mf::launch_kernel(mf::permute_rows_kernel, dim3(grid), dim3(mf::kRowThreads), 0,
+                                static_cast<cudaStream_t>(stream), true, static_cast<const uint8_t*>(recv), pitch,
+                                entry_row, plan, static_cast<uint4*>(xg), H, n_rows);
+}
+

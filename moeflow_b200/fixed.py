@@ -519,6 +519,17 @@ class FixedEPLayer:
 
             self._tmap_act = make_tile_tmap(self.act, self.block_m)
             self._a_gemm2.b_tmap = C.addressof(self._tmap_act)
+        # Opt-in (gemm_kwargs permute_rows=True): copy the received hidden rows into expert-major order first,
+        # so that the gate/up GEMM reads token tiles by TMA too instead of gathering them by entry index.
+        self.permute_rows = bool(self.gemm_kwargs.get("permute_rows", False))
+        if self.permute_rows:
+            from .ops.kernels import make_tile_tmap
+
+            self._xg = torch.zeros(max(N, self.block_m), H, dtype=torch.bfloat16, device=dev)
+            self._tmap_xg = make_tile_tmap(self._xg, self.block_m)
+            g1 = self._a_gemm1
+            g1.b_base, g1.b_pitch, g1.b_index = self._xg.data_ptr(), H * 2, None
+            g1.b_tmap = C.addressof(self._tmap_xg)
         # Owner reduce + return push can run inside the down GEMM (gemm_kwargs fuse_return=True: four extra
         # warps reduce a row as soon as its last slot is written and store it into the source rank's
         # buffer) or as the separate owner_reduce_push kernel chained by programmatic launch.  Measured on
@@ -693,6 +704,10 @@ class FixedEPLayer:
                 return
             _lib.check(lib.mf_owner_reduce_push(C.byref(self._a_reduce), s), "owner_reduce_push")
             return
+        if self.permute_rows:
+            _lib.check(self._lib.mf_permute_rows(self._recv_store.data_ptr(), self.pitch * 2, self.entry_row.data_ptr(),
+                                                 self.plan.data_ptr(), self._xg.data_ptr(), self.H, self.world * self.C,
+                                                 min(self.n_entries, 8 * self.n_sms), s), "permute rows")
         _lib.check(self._lib.mf_gemm_gate_up(self._tmap13, C.byref(self._a_gemm1), self.block_m, self.n_sms, s), "gate/up gemm")
         if stop_after == "GEMM1":
             return

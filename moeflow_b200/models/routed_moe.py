@@ -26,7 +26,7 @@ class GraphedMoELayer:
         self._warmup = warmup
         # route+dispatch, meta (two launches in its multi-CTA form), gate/up, down(+reduce+push), combine
         self.kernels_per_step = (5 if getattr(layer, "fuse_return", False) else 6) + (
-            1 if getattr(layer, "meta_ctas", 1) > 1 else 0)
+            1 if getattr(layer, "meta_ctas", 1) > 1 else 0) + (1 if getattr(layer, "permute_rows", False) else 0)
 
     def _forward(self) -> torch.Tensor:
         return self.layer.forward(self.x, self.logits, self.bias, self.num_valid)

@@ -221,6 +221,7 @@ def lib() -> C.CDLL:
         "mf_dispatch_push": [C.POINTER(DispatchArgs), P],
         "mf_expert_meta": [C.POINTER(MetaArgs), P],
         "mf_plan_split": [I, I, I, I, I, I],
+        "mf_permute_rows": [P, LL, P, P, P, I, I, I, P],
         "mf_owner_reduce_push": [C.POINTER(ReducePushArgs), P],
         "mf_combine": [C.POINTER(CombineArgs), P],
         "mf_expert_prepare": [P, LL, I, I, I, I, I, P, P, P, P, P],

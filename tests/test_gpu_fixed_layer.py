@@ -376,3 +376,25 @@ def test_external_expert_function_on_the_cuda_backend(world, mode):
 
     torch.cuda.synchronize()
     assert bitwise_equal(got, combine_partials(cu[0].ret_recv, cu[0].hit, torch.bfloat16, 0, "bf16_ring"))
+
+
+@pytest.mark.parametrize("world,cap,experts,top_k", [(1, 16, 16, 4), (2, 32, 16, 4), (1, 512, 16, 4)])
+def test_expert_major_copy_with_tma_token_tiles_equals_the_gather_bitwise(world, cap, experts, top_k):
+    """gemm_kwargs permute_rows=True: received rows copied into expert-major order, gate/up token tiles by TMA.
+    The last case has 128 expected rows per expert, i.e. 128-row tiles."""
+    cfg = replace(SMALL_GPU, n_routed_experts=experts, top_k=top_k)
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    tokens = [cap - 3, cap // 2][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 17)
+    base = _layers(cfg, world, cap, w13, w2, "cuda")
+    perm = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"permute_rows": True})
+    assert perm[0].permute_rows and perm[0].block_m == base[0].block_m
+    for rep in range(2):
+        outs_a = simulate_fixed(base, xs, lgs, bias)
+        outs_b = simulate_fixed(perm, xs, lgs, bias)
+        torch.cuda.synchronize()
+        for ly in base + perm:
+            _ok(ly)
+        for a, b in zip(outs_a, outs_b):
+            assert bitwise_equal(a, b)
