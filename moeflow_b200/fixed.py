@@ -429,7 +429,6 @@ class FixedEPLayer:
             raise ValueError("block_m must be 32, 64 or 128")
         self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
         self.max_tiles = (N + self.block_m - 1) // self.block_m + L
-        self.max_split_slots = 2 * self.n_sms
         self.out = torch.zeros(Cc, H, dtype=torch.bfloat16, device=dev)
         self.hit = torch.zeros(Cc, R, dtype=torch.uint8, device=dev)
         self._route_w = torch.zeros(Cc, K, dtype=torch.float32, device=dev)
