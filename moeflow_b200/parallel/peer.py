@@ -83,6 +83,28 @@ class SymmetricRegion:
         self.local.release()
 
 
+def check_exchange(gathered: list, world: int, nbytes: int) -> None:
+    """Validate what the ranks exchanged at bootstrap: ``(rank, nbytes, 64-byte IPC handle)`` per rank.
+
+    Every rank runs this on the same gathered list, so a rank that asked for a different size (for instance a
+    different capacity) or sent a malformed handle makes all ranks raise the same error before any peer memory
+    is mapped, instead of leaving some of them waiting.
+    """
+    if len(gathered) != world:
+        raise RuntimeError(f"symmetric allocation: expected {world} bootstrap records, got {len(gathered)}")
+    for r, record in enumerate(gathered):
+        if not isinstance(record, tuple) or len(record) != 3:
+            raise RuntimeError(f"symmetric allocation: malformed bootstrap record from rank {r}")
+        peer_rank, peer_bytes, handle = record
+        if peer_rank != r or peer_bytes != nbytes:
+            raise RuntimeError(
+                f"symmetric allocation mismatch: rank {r} reported rank {peer_rank}, {peer_bytes} bytes, "
+                f"expected {nbytes}"
+            )
+        if not isinstance(handle, (bytes, bytearray)) or len(handle) != 64:
+            raise RuntimeError(f"symmetric allocation: rank {r} sent a malformed IPC handle")
+
+
 def _alloc(nbytes: int) -> _RawDeviceMemory:
     out = C.c_void_p()
     _lib.check(_lib.lib().mf_peer_alloc(C.byref(out), nbytes), "peer alloc")
@@ -112,13 +134,9 @@ class PeerGroup:
             _lib.check(_lib.lib().mf_peer_export(C.c_void_p(mine.ptr), handle), "peer export")
             gathered: list = [None] * self.world
             dist.all_gather_object(gathered, (self.rank, nbytes, bytes(handle)), group=self.group)
+            check_exchange(gathered, self.world, nbytes)
             ptrs, keep = [], []
             for r, (peer_rank, peer_bytes, peer_handle) in enumerate(gathered):
-                if peer_rank != r or peer_bytes != nbytes:
-                    raise RuntimeError(
-                        f"symmetric allocation mismatch: rank {r} reported rank {peer_rank}, {peer_bytes} bytes, "
-                        f"expected {nbytes}"
-                    )
                 if r == self.rank:
                     ptrs.append(mine.ptr)
                     continue
