@@ -66,3 +66,60 @@ def test_peer_memory_ping_and_bounded_wait():
     info = _probe("peer", _ranks())
     assert info["ok"], info
     assert all(r["timeout_code"] == 8 for r in info["ranks"])
+
+
+def test_peer_ping_bounded_wait_on_one_gpu():
+    """Two simulated ranks on one GPU, their kernels launched one after the other (never concurrently): rank 0
+    pings first and its wait for rank 1's word runs out with the time-out status; rank 1 then finds both words;
+    a second ping of rank 0 succeeds, i.e. the context survived the time-out."""
+    from moeflow_b200.ops._lib import decode_status
+    from moeflow_b200.parallel.peer import PeerGroup, ping
+
+    regions = PeerGroup.local(2, 4096)
+    status = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(2)]
+    ping(regions[0], 0, 1, status[0], wait_ns=20_000_000)
+    ping(regions[1], 0, 1, status[1], wait_ns=20_000_000)
+    torch.cuda.synchronize()
+    first, second = decode_status(int(status[0].item())), decode_status(int(status[1].item()))
+    assert first["code"] == 8 and first["who"] == 1, first
+    assert second["code"] == 0, second
+    status[0].zero_()
+    ping(regions[0], 0, 1, status[0], wait_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert decode_status(int(status[0].item()))["code"] == 0
+
+
+def test_a_missing_peer_is_reported_by_the_layer_status_word_and_nothing_hangs():
+    """Rank 0 of a simulated pair runs a whole forward alone: rank 1 never dispatches, so the metadata kernel's
+    bounded wait for its flag runs out (50 ms), the layer records who was missing and carries on to the end.
+    A fresh pair of layers then runs normally on the same context."""
+    from conftest import SMALL_GPU
+    from moeflow_b200.ep_moe import shard_experts
+    from moeflow_b200.fixed import FixedEPLayer, simulate_fixed
+    from moeflow_b200.parallel.peer import PeerGroup
+    from moeflow_b200.testing import make_bias, make_hidden, make_logits, make_weights
+
+    cfg, cap = SMALL_GPU, 8
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+
+    def pair():
+        regions = PeerGroup.local(2, FixedEPLayer.peer_bytes(cfg, 2, cap))
+        return [FixedEPLayer(cfg, r, 2, *shard_experts(w13, w2, r, 2), capacity=cap, backend="cuda",
+                             peer_region=regions[r], wait_ns=50_000_000) for r in range(2)]
+
+    xs = [make_hidden(cap, cfg, 5 + r, device="cuda") for r in range(2)]
+    lgs = [make_logits(cap, cfg, 50 + r, device="cuda") for r in range(2)]
+    lonely = pair()[0]
+    hit = lonely.stage_pack(xs[0], lgs[0], bias)
+    lonely.stage_experts()
+    out = lonely.stage_combine(hit, xs[0].dtype)
+    torch.cuda.synchronize()
+    st = lonely.check_status()
+    assert st["code"] == 1 and st["who"] == 1, st  # dispatch flag of source rank 1 never arrived
+    assert out.shape == (cap, cfg.hidden_size)
+    fresh = pair()
+    outs = simulate_fixed(fresh, xs, lgs, bias)
+    torch.cuda.synchronize()
+    assert all(ly.check_status()["code"] == 0 for ly in fresh)
+    assert all(torch.isfinite(o.float()).all() for o in outs)
