@@ -4,8 +4,6 @@ Counterpart of ``scripts/bench/inputs.py:8-23``.
 
 from __future__ import annotations
 
-import torch
-
 from ..config import MoEConfig
 from ..testing import make_bias, make_weights
 

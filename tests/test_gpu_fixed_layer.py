@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from conftest import SMALL_GPU, replace
-from moeflow_b200.ep_moe import EPMoELayer, shard_experts, simulate_ep
+from moeflow_b200.ep_moe import shard_experts
 from moeflow_b200.fixed import FixedEPLayer, simulate_fixed
 from moeflow_b200.reference import moe_reference
 from moeflow_b200.testing import make_bias, make_hidden, make_logits, make_weights
