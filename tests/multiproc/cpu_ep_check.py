@@ -76,6 +76,26 @@ def main() -> int:
     if err > 1e-5:
         fails.append(f"oracle error {err:.2e}")
 
+    # The engine-facing transport core with stand-in experts (global expert g scales by g + 1): what comes back
+    # must equal the closed form sum_k w_k * (id_k + 1) * x, and foreign slots must point at the filler expert.
+    from moeflow_b200.integrations.row_transport import VariableRowTransport
+    from moeflow_b200.router import route
+
+    transport = VariableRowTransport(CollectiveRowExchange(), CFG.experts_per_rank(world))
+    tw, tids = route(lgs[rank], None, CFG)
+    got = transport.scatter(xs[rank], tw, tids, CFG.n_routed_experts)
+    lo, hi = transport.first_expert, transport.first_expert + transport.num_local_experts
+    mine = (got.expert_ids >= lo) & (got.expert_ids < hi)
+    if not bool(((got.weights == 0) | mine).all()):
+        fails.append("a slot of another rank kept a non-zero weight")
+    if int(got.rows_per_local_expert.sum()) != int(mine.sum()):
+        fails.append("rows per local expert do not add up to the local slots")
+    gain = (torch.where(mine, got.expert_ids + 1, 0).to(torch.float32) * got.weights).sum(dim=1, keepdim=True)
+    back = transport.gather(gain * got.hidden, torch.float32, wire_dtype=torch.float32)
+    want = ((tids + 1).to(torch.float32) * tw).sum(dim=1, keepdim=True) * xs[rank]
+    if not torch.allclose(back, want, rtol=1e-5, atol=1e-6) or transport.busy:
+        fails.append("row transport round trip differs from the closed form")
+
     detected = None
     if args.drop_rank >= 0:
         # The leaving rank exits between steps; the others learn of it when their next collective times out.

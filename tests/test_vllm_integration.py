@@ -385,3 +385,33 @@ def test_runner_class_follows_the_installed_engine_interface(monkeypatch):
                                              shared_experts_input=None)
     assert seen["layer"] is layer and runner.routed_experts is layer and torch.equal(out, x + 1)
     assert "routed_experts" not in dict(runner.named_children())
+
+
+def test_row_transport_round_trip_and_reentry_guard():
+    """World 1 with a loop-back exchange: every slot is local, ids come back global, the per-expert row counts
+    are the histogram of the routing, and gather() merges the partial rows per token."""
+    from moeflow_b200.integrations.row_transport import VariableRowTransport
+    from moeflow_b200.router import route
+
+    class Loopback:
+        rank, world = 0, 1
+
+        def exchange_counts(self, counts):
+            return counts.clone()
+
+        def exchange(self, rows, send_counts, recv_counts):
+            return rows.clone()
+
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(5, SMALL.hidden_size, generator=g)
+    w, ids = route(torch.randn(5, SMALL.n_routed_experts, generator=g), None, SMALL)
+    t = VariableRowTransport(Loopback(), SMALL.n_routed_experts)
+    got = t.scatter(x, w, ids, SMALL.n_routed_experts)
+    assert t.busy and torch.equal(got.hidden, x) and torch.equal(got.expert_ids, ids) and torch.equal(got.weights, w)
+    assert torch.equal(got.rows_per_local_expert.long(), torch.bincount(ids.flatten().long(), minlength=SMALL.n_routed_experts))
+    with pytest.raises(RuntimeError, match="not re-entrant"):
+        t.scatter(x, w, ids, SMALL.n_routed_experts)
+    out = t.gather(got.hidden * got.weights.sum(dim=1, keepdim=True), torch.float32, wire_dtype=torch.float32)
+    torch.testing.assert_close(out, x * w.sum(dim=1, keepdim=True))
+    with pytest.raises(RuntimeError, match="without a matching"):
+        t.gather(out, torch.float32)
