@@ -159,3 +159,20 @@ def test_report_generators_refuse_bad_records(tmp_path):
                         '"2","void at::native::fill(int)","gpu__time_duration.sum","ns","1,000"\n')
     text = S.launches_summary(str(csv_path))
     assert "mf::combine_kernel | 2 | 1.00 | 5.0" in text and "library helper kernels (at::native): 1" in text
+
+
+def test_weight_source_specs_and_profiler_window():
+    from moeflow_b200.bench.inputs import WeightSource, load_weights
+    from moeflow_b200.bench.profiling import profile_layer
+    from moeflow_b200.config import MoEConfig
+
+    assert WeightSource.parse("synthetic") == WeightSource("synthetic")
+    assert WeightSource.parse("real:17") == WeightSource("real", 17)
+    for bad in ("", "real", "real:x", "synthetic:3", "file.pt"):
+        with pytest.raises(ValueError):
+            WeightSource.parse(bad)
+    cfg = MoEConfig(hidden_size=16, moe_intermediate_size=8, n_routed_experts=4, top_k=2)
+    w13, w2, bias = load_weights("synthetic", cfg, "cpu", experts=range(1, 3))
+    assert w13.shape == (2, 16, 16) and w2.shape == (2, 16, 8) and bias.shape == (4,)
+    with profile_layer("nothing to record", enabled=False) as window:
+        assert not window.active
