@@ -35,3 +35,16 @@ def test_thresholds():
     assert abs(normwise_rel_err(torch.tensor([3.0, 4.5]), ref) - 0.1) < 1e-12
     assert normwise_rel_err(torch.tensor([1.0]), torch.tensor([0.0])) == 1.0
     assert calc_diff(ref, ref) == 0.0
+
+
+def test_first_difference_points_at_the_first_differing_element():
+    from moeflow_b200.tolerances import first_difference
+
+    a = torch.tensor([1.0, 0.0, 3.0, 4.0])
+    assert first_difference(a, a.clone()) is None
+    b = a.clone()
+    b[1], b[3] = -0.0, 5.0
+    where = first_difference(a, b)
+    assert where["index"] == 1 and where["count"] == 2 and where["b"] == 0.0
+    assert "reason" in first_difference(a, a.to(torch.bfloat16))
+    assert first_difference(torch.empty(0), torch.empty(0)) is None
