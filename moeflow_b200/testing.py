@@ -1,93 +1,108 @@
-"""Deterministic synthetic inputs: expert weights, hidden states, routing distributions.
+"""Seeded synthetic inputs for tests and benchmarks: expert weights, hidden rows, a selection bias, and router
+logits whose top-k choice follows a chosen popularity profile.
 
-All generators draw on the CPU from a seeded ``torch.Generator`` so that every rank and every
-backend sees the same numbers.  Counterpart of the reference's ``moeflow/testing.py:14-80``.
+Everything is drawn on the CPU from a ``torch.Generator`` seeded by the caller and only then moved to the
+target device, so every rank and every backend sees the same numbers whatever hardware it runs on.
+
+Popularity profiles (``make_logits(dist=...)``); each is an additive offset on i.i.d. normal logits:
+
+    uniform   no offset
+    zipf      the expert of popularity rank r gets ``-2 s ln r``; ranks are a random permutation of the experts,
+              or follow the expert id (``hot_first``), which puts all popular experts on the first EP rank
+    hotspot   the first ``hot_experts`` experts (default: top_k) get +20, all others -20, so they win every token
+
+Counterpart of ``moeflow/testing.py:14-80`` of the reference.
 """
 
 from __future__ import annotations
 
 import math
+from typing import Callable
 
 import torch
 
 from .config import MoEConfig
 
-DISTRIBUTIONS = ("uniform", "zipf", "hotspot")
 
-
-def _gen(seed: int) -> torch.Generator:
+def _generator(seed: int) -> torch.Generator:
     return torch.Generator(device="cpu").manual_seed(int(seed))
 
 
-def make_weights(cfg: MoEConfig, seed: int, device="cpu", dtype=torch.bfloat16, experts: range | None = None):
-    """``w13 [E, 2I, H]`` ~ N(0, (2/sqrt(H))^2), ``w2 [E, H, I]`` ~ N(0, (1/sqrt(I))^2).
-
-    The scales keep activations O(1) and make the SwiGLU clamp bite now and then.  With ``experts``
-    only that slice is materialised (expert e always gets the same numbers, whatever the slice).
-    """
-    n_exp, hidden, inter = cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size
-    if experts is None:
-        g = _gen(seed)
-        w13 = torch.randn(n_exp, 2 * inter, hidden, generator=g) * (2.0 / math.sqrt(hidden))
-        w2 = torch.randn(n_exp, hidden, inter, generator=g) * (1.0 / math.sqrt(inter))
-        return w13.to(device=device, dtype=dtype), w2.to(device=device, dtype=dtype)
-    w13 = torch.empty(len(experts), 2 * inter, hidden, dtype=dtype, device=device)
-    w2 = torch.empty(len(experts), hidden, inter, dtype=dtype, device=device)
-    for i, e in enumerate(experts):
-        g = _gen(seed * 1_000_003 + e)
-        w13[i] = (torch.randn(2 * inter, hidden, generator=g) * (2.0 / math.sqrt(hidden))).to(dtype)
-        w2[i] = (torch.randn(hidden, inter, generator=g) * (1.0 / math.sqrt(inter))).to(dtype)
+# ---- weights, hidden rows, bias -----------------------------------------------------------------------
+def _gate_up_and_down(cfg: MoEConfig, experts: int, gen: torch.Generator):
+    """fp32 ``w13 [experts, 2I, H]`` with std ``2/sqrt(H)`` and ``w2 [experts, H, I]`` with std ``1/sqrt(I)``:
+    activations stay O(1) and the SwiGLU clamp bites now and then."""
+    hidden, inter = cfg.hidden_size, cfg.moe_intermediate_size
+    w13 = torch.randn(experts, 2 * inter, hidden, generator=gen).mul_(2.0 / math.sqrt(hidden))
+    w2 = torch.randn(experts, hidden, inter, generator=gen).mul_(1.0 / math.sqrt(inter))
     return w13, w2
 
 
+def make_weights(cfg: MoEConfig, seed: int, device="cpu", dtype=torch.bfloat16, experts: range | None = None):
+    """All experts from one stream, or (``experts`` given) only those, each from its own stream
+    ``seed * 1_000_003 + e`` so that expert e gets the same numbers whichever slice asks for it."""
+    if experts is None:
+        w13, w2 = _gate_up_and_down(cfg, cfg.n_routed_experts, _generator(seed))
+        return w13.to(device=device, dtype=dtype), w2.to(device=device, dtype=dtype)
+    blocks = [_gate_up_and_down(cfg, 1, _generator(seed * 1_000_003 + e)) for e in experts]
+    stack = lambda which: torch.cat([b[which] for b in blocks]).to(device=device, dtype=dtype)  # noqa: E731
+    if not blocks:
+        empty13, empty2 = _gate_up_and_down(cfg, 0, _generator(seed))
+        return empty13.to(device=device, dtype=dtype), empty2.to(device=device, dtype=dtype)
+    return stack(0), stack(1)
+
+
 def make_hidden(num_tokens: int, cfg: MoEConfig, seed: int, device="cpu", dtype=torch.bfloat16):
-    return torch.randn(num_tokens, cfg.hidden_size, generator=_gen(seed)).to(device=device, dtype=dtype)
-
-
-def make_logits(
-    num_tokens: int,
-    cfg: MoEConfig,
-    seed: int,
-    dist: str = "uniform",
-    device="cpu",
-    zipf_s: float = 1.2,
-    hot_experts: int | None = None,
-    hot_first: bool = False,
-):
-    """Router logits ``[T, E]`` fp32 whose top-k choice follows a popularity profile.
-
-    ``uniform``: i.i.d. normal.  ``zipf``: expert with popularity rank r gets an offset
-    ``-2 * s * log(r)``; ranks are a random permutation of the experts, or 1..E in id order with
-    ``hot_first`` (the popular experts then share one EP rank).  ``hotspot``: the first
-    ``hot_experts`` (default ``top_k``) experts win every token.
-    """
-    g = _gen(seed)
-    n_exp = cfg.n_routed_experts
-    logits = torch.randn(num_tokens, n_exp, generator=g)
-    if dist == "uniform":
-        pass
-    elif dist == "zipf":
-        order = torch.randperm(n_exp, generator=g)
-        if hot_first:
-            order = torch.arange(n_exp)
-        rank_of = torch.empty(n_exp)
-        rank_of[order] = torch.arange(1, n_exp + 1, dtype=torch.float32)
-        logits = logits - 2.0 * zipf_s * torch.log(rank_of)
-    elif dist == "hotspot":
-        hot = cfg.top_k if hot_experts is None else hot_experts
-        logits[:, :hot] += 20.0
-        logits[:, hot:] -= 20.0
-    else:
-        raise ValueError(f"unknown routing distribution {dist!r}")
-    return logits.to(device=device, dtype=torch.float32)
+    return torch.randn(num_tokens, cfg.hidden_size, generator=_generator(seed)).to(device=device, dtype=dtype)
 
 
 def make_bias(cfg: MoEConfig, seed: int, device="cpu"):
-    return (0.05 * torch.randn(cfg.n_routed_experts, generator=_gen(seed))).to(device=device, dtype=torch.float32)
+    """A small selection bias (std 0.05), enough to reorder close scores."""
+    draw = torch.randn(cfg.n_routed_experts, generator=_generator(seed))
+    return draw.mul_(0.05).to(device=device, dtype=torch.float32)
 
 
+# ---- router logits --------------------------------------------------------------------------------------
+def _no_offset(cfg, gen, **_):
+    return 0.0
+
+
+def _zipf_offset(cfg, gen, zipf_s: float, hot_first: bool, **_):
+    by_popularity = torch.randperm(cfg.n_routed_experts, generator=gen)  # drawn even when unused: keeps streams aligned
+    if hot_first:
+        by_popularity = torch.arange(cfg.n_routed_experts)
+    rank = torch.empty(cfg.n_routed_experts)
+    rank[by_popularity] = torch.arange(1, cfg.n_routed_experts + 1, dtype=torch.float32)
+    return -2.0 * zipf_s * rank.log()
+
+
+def _hotspot_offset(cfg, gen, hot_experts: int | None, **_):
+    hot = cfg.top_k if hot_experts is None else hot_experts
+    offset = torch.full((cfg.n_routed_experts,), -20.0)
+    offset[:hot] = 20.0
+    return offset
+
+
+_PROFILES: dict[str, Callable] = {"uniform": _no_offset, "zipf": _zipf_offset, "hotspot": _hotspot_offset}
+DISTRIBUTIONS = tuple(_PROFILES)
+
+
+def make_logits(num_tokens: int, cfg: MoEConfig, seed: int, dist: str = "uniform", device="cpu", zipf_s: float = 1.2,
+                hot_experts: int | None = None, hot_first: bool = False):
+    """fp32 router logits ``[T, E]``: i.i.d. normal plus the profile's per-expert offset."""
+    if dist not in _PROFILES:
+        raise ValueError(f"unknown routing distribution {dist!r}")
+    gen = _generator(seed)
+    noise = torch.randn(num_tokens, cfg.n_routed_experts, generator=gen)
+    offset = _PROFILES[dist](cfg, gen, zipf_s=zipf_s, hot_first=hot_first, hot_experts=hot_experts)
+    return (noise + offset).to(device=device, dtype=torch.float32)
+
+
+# ---- a stand-in expert backend ----------------------------------------------------------------------------
 class ScaleExperts:
-    """Hand-checkable expert backend: global expert ``g`` maps ``x`` to ``(g + 1) * x``."""
+    """Expert backend one can check by hand: global expert ``g`` maps a row ``x`` to ``(g + 1) * x``
+    (times the row's routing weight when one is passed).  Takes the expert-major rows and offsets of the
+    variable-size pipeline like every ``ExpertCompute``; the weights are ignored."""
 
     name = "scale"
 
@@ -95,11 +110,11 @@ class ScaleExperts:
         self.offset = rank_expert_offset
 
     def __call__(self, a, expert_offsets, w13, w2, swiglu_limit, row_weight=None):
-        bounds = expert_offsets.tolist()
-        out = torch.empty_like(a)
-        for e, (lo, hi) in enumerate(zip(bounds[:-1], bounds[1:])):
-            y = a[lo:hi].to(torch.float32) * float(self.offset + e + 1)
-            if row_weight is not None:
-                y = y * row_weight[lo:hi].unsqueeze(1)
-            out[lo:hi] = y.to(a.dtype)
-        return out
+        rows_per_expert = expert_offsets[1:] - expert_offsets[:-1]
+        local_expert = torch.repeat_interleave(torch.arange(rows_per_expert.numel(), device=a.device),
+                                               rows_per_expert.to(torch.int64), output_size=a.shape[0])
+        gain = (local_expert + (self.offset + 1)).to(torch.float32)
+        scaled = a.to(torch.float32) * gain[:, None]
+        if row_weight is not None:
+            scaled = scaled * row_weight[:, None]
+        return scaled.to(a.dtype)
