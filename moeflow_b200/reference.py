@@ -1,12 +1,16 @@
-"""Loop-level oracle for one routed MoE layer.
+"""The oracle: one routed MoE layer computed the slowest and most obvious way.
 
-Boundary: hidden states ``x [T, H]``, router logits ``[T, E]`` (fp32) and the optional selection bias
-``[E]`` go in; the weighted sum of the selected routed experts (routed scaling factor included)
-comes out in ``x.dtype``.  Gate GEMM, shared expert and norms are outside.
+In:  hidden rows ``x [T, H]``, router logits ``[T, E]``, optionally the selection bias ``[E]``, and the expert
+weights ``w13 [E, 2I, H]`` (gate rows, then up rows) and ``w2 [E, H, I]``.
+Out: for every token the sum over its K chosen experts of ``weight * expert(x)``, the routed scaling factor
+included, in ``x.dtype``.  The gate projection that produces the logits, the shared expert and the norms are
+not part of this boundary.
 
-Everything here is written one token and one expert at a time with plain Python loops and scalar
-float64 scoring.  It shares no indexing code with the router, dispatch or GEMM implementations it is
-used to check.  Behavioural counterpart of the reference's ``moeflow/reference.py:21-127``.
+Nothing here is vectorised over tokens or experts and nothing is sorted: scores are Python floats (fp64),
+"the best k" is found by scanning k times for the largest remaining value (a strict ``>`` keeps the lower
+index on ties), and every (token, expert) pair is one pair of matrix-vector products.  The module shares no
+indexing code with the router, the dispatch stages or the kernels, which is what makes it usable as their
+judge.  Same semantics as ``moeflow/reference.py:21-127`` of the reference.
 """
 
 from __future__ import annotations
@@ -20,111 +24,128 @@ from .config import MoEConfig
 Route = list[tuple[int, float]]
 
 
-def _scores(logit_row: torch.Tensor, kind: str) -> list[float]:
-    raw = logit_row.detach().to(torch.float64).cpu().tolist()
-    if kind == "sigmoid":
-        return [1.0 / (1.0 + math.exp(-v)) for v in raw]
-    if kind == "softmax":
-        top = max(raw)
-        expd = [math.exp(v - top) for v in raw]
-        total = math.fsum(expd)
-        return [v / total for v in expd]
-    raise ValueError(f"unknown scoring function {kind!r}")
+# ---- routing ----------------------------------------------------------------------------------------------
+def _sigmoid_scores(z: list[float]) -> list[float]:
+    return [1.0 / (1.0 + math.exp(-v)) for v in z]
+
+
+def _softmax_scores(z: list[float]) -> list[float]:
+    peak = max(z)
+    grown = [math.exp(v - peak) for v in z]
+    whole = math.fsum(grown)
+    return [g / whole for g in grown]
+
+
+_SCORING = {"sigmoid": _sigmoid_scores, "softmax": _softmax_scores}
+
+
+def _scan_best(values: list[float], how_many: int, allowed=None) -> list[int]:
+    """Indices of the ``how_many`` largest values, best first; among equals the lower index comes first."""
+    taken: list[int] = []
+    for _ in range(min(how_many, len(values))):
+        best = None
+        for i, v in enumerate(values):
+            if i in taken or (allowed is not None and i not in allowed):
+                continue
+            if best is None or v > values[best]:
+                best = i
+        if best is None:
+            break
+        taken.append(best)
+    return taken
 
 
 def route_token(logits: torch.Tensor, bias: torch.Tensor | None, cfg: MoEConfig) -> Route:
-    """Route one token; returns ``[(expert, weight)]`` in selection order (best biased score first).
+    """``[(expert, weight), ...]`` of one token, best selection key first.
 
-    The selection uses ``score + bias``; the returned weight is the *unbiased* score, renormalised by
-    ``sum + 1e-20`` when ``norm_topk_prob`` and multiplied by ``routed_scaling_factor``.  With expert
-    groups, a group's rank is the sum of its two best biased scores when a bias is given and its best
-    score otherwise, and only ``topk_group`` groups stay eligible.  Equal scores go to the lower id.
+    key = score + bias decides who is picked; the weight is the *unbiased* score, divided by the picks' sum
+    (+1e-20) under ``norm_topk_prob``, times ``routed_scaling_factor``.  With expert groups only the
+    ``topk_group`` best groups are eligible; a group is rated by its two best keys added up when there is a
+    bias and by its best key when there is none.
     """
-    n_experts = logits.numel()
-    score = _scores(logits, cfg.scoring_func)
-    shift = [0.0] * n_experts if bias is None else bias.detach().to(torch.float64).cpu().tolist()
-    key = [score[e] + shift[e] for e in range(n_experts)]
+    if cfg.scoring_func not in _SCORING:
+        raise ValueError(f"unknown scoring function {cfg.scoring_func!r}")
+    score = _SCORING[cfg.scoring_func](logits.detach().to(torch.float64).cpu().tolist())
+    experts = len(score)
+    if bias is None:
+        key = list(score)
+    else:
+        key = [s + b for s, b in zip(score, bias.detach().to(torch.float64).cpu().tolist())]
 
-    width = n_experts // cfg.n_group
-    ranked_groups = []
+    per_group = experts // cfg.n_group
+    rating = []
     for g in range(cfg.n_group):
-        best_first = sorted(key[g * width : (g + 1) * width], reverse=True)
-        strength = best_first[0] + best_first[1] if bias is not None else best_first[0]
-        ranked_groups.append((-strength, g))
-    ranked_groups.sort()
-    open_groups = {g for _, g in ranked_groups[: cfg.topk_group]}
+        members = key[g * per_group:(g + 1) * per_group]
+        first = _scan_best(members, 1)[0]
+        if bias is None:
+            rating.append(members[first])
+        else:
+            second = _scan_best(members, 2)[1]
+            rating.append(members[first] + members[second])
+    eligible_groups = set(_scan_best(rating, cfg.topk_group))
+    eligible = {e for e in range(experts) if e // per_group in eligible_groups}
 
-    order = sorted((e for e in range(n_experts) if e // width in open_groups), key=lambda e: (-key[e], e))
-    picked = order[: cfg.top_k]
-    w = [score[e] for e in picked]
+    picks = _scan_best(key, cfg.top_k, allowed=eligible)
+    weights = [score[e] for e in picks]
     if cfg.norm_topk_prob:
-        denom = sum(w) + 1e-20
-        w = [v / denom for v in w]
-    return [(e, v * cfg.routed_scaling_factor) for e, v in zip(picked, w)]
+        whole = sum(weights) + 1e-20
+        weights = [w / whole for w in weights]
+    return [(e, w * cfg.routed_scaling_factor) for e, w in zip(picks, weights)]
 
 
 def route_reference(logits: torch.Tensor, bias: torch.Tensor | None, cfg: MoEConfig) -> list[Route]:
-    return [route_token(logits[t], bias, cfg) for t in range(logits.shape[0])]
+    return [route_token(row, bias, cfg) for row in logits]
 
 
+# ---- experts ------------------------------------------------------------------------------------------------
 def swiglu_clamp(gate: torch.Tensor, up: torch.Tensor, limit: float | None) -> torch.Tensor:
-    """``silu(gate) * up`` with the gate clamped from above and the up branch clamped both ways."""
+    """``silu(gate) * up``; with a limit the gate is capped from above and the up branch on both sides."""
     if limit is not None:
-        gate = gate.clamp(max=limit)
-        up = up.clamp(min=-limit, max=limit)
+        gate, up = gate.clamp(max=limit), up.clamp(min=-limit, max=limit)
     return gate * torch.sigmoid(gate) * up
 
 
-def expert_forward(
-    x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, limit: float | None, acc_dtype: torch.dtype = torch.float32
-) -> torch.Tensor:
-    """One token through one expert: ``x [H]``, ``w13 [2I, H] = [gate; up]``, ``w2 [H, I]`` -> ``[H]``."""
+def expert_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, limit: float | None,
+                   acc_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """One token ``x [H]`` through one expert (``w13 [2I, H]``, ``w2 [H, I]``) -> ``[H]`` in ``acc_dtype``."""
+    gate_and_up = torch.mv(w13.to(acc_dtype), x.to(acc_dtype))
     inter = w2.shape[1]
-    hidden = torch.mv(w13.to(acc_dtype), x.to(acc_dtype))
-    act = swiglu_clamp(hidden[:inter], hidden[inter:], limit)
-    return torch.mv(w2.to(acc_dtype), act)
+    return torch.mv(w2.to(acc_dtype), swiglu_clamp(gate_and_up[:inter], gate_and_up[inter:], limit))
 
 
-def moe_reference(
-    x: torch.Tensor,
-    logits: torch.Tensor,
-    bias: torch.Tensor | None,
-    w13: torch.Tensor,
-    w2: torch.Tensor,
-    cfg: MoEConfig,
-    acc_dtype: torch.dtype = torch.float32,
-    routes: list[Route] | None = None,
-) -> torch.Tensor:
-    """Whole layer: ``w13 [E, 2I, H]``, ``w2 [E, H, I]`` -> ``[T, H]`` in ``x.dtype``.
-
-    ``routes`` replaces the routing, so that the expert/combine path can be judged on exactly the
-    expert choice of the implementation under test.
-    """
-    n_tokens, hidden = x.shape
-    out = torch.zeros(n_tokens, hidden, dtype=acc_dtype, device=x.device)
-    for t in range(n_tokens):
-        chosen = route_token(logits[t], bias, cfg) if routes is None else routes[t]
-        total = torch.zeros(hidden, dtype=acc_dtype, device=x.device)
-        for expert, weight in chosen:
-            total = total + weight * expert_forward(x[t], w13[expert], w2[expert], cfg.swiglu_limit, acc_dtype)
-        out[t] = total
-    return out.to(x.dtype)
+def moe_reference(x: torch.Tensor, logits: torch.Tensor, bias: torch.Tensor | None, w13, w2, cfg: MoEConfig,
+                  acc_dtype: torch.dtype = torch.float32, routes: list[Route] | None = None) -> torch.Tensor:
+    """The whole layer.  ``routes`` (one per token) replaces the routing step, so that the expert and combine
+    path of an implementation can be judged on exactly the experts that implementation chose.
+    ``w13`` / ``w2`` only need ``__getitem__`` by expert id (a tensor, or a lookup of the few experts needed)."""
+    rows = []
+    for t in range(x.shape[0]):
+        route = routes[t] if routes is not None else route_token(logits[t], bias, cfg)
+        acc = torch.zeros(x.shape[1], dtype=acc_dtype, device=x.device)
+        for expert, weight in route:
+            acc = acc + weight * expert_forward(x[t], w13[expert], w2[expert], cfg.swiglu_limit, acc_dtype)
+        rows.append(acc)
+    if not rows:
+        return torch.zeros(0, x.shape[1], dtype=x.dtype, device=x.device)
+    return torch.stack(rows).to(x.dtype)
 
 
+# ---- dispatch contract ------------------------------------------------------------------------------------------
 def ep_dispatch_reference(routes_per_rank: list[list[Route]], experts_per_rank: int) -> list[list]:
-    """What every destination rank must receive: one copy per (token, destination rank).
+    """What every rank has to receive: one copy of a token per destination rank that owns one of its experts.
 
-    ``routes_per_rank[src][t]`` is the route of token ``t`` owned by rank ``src``.  The result
-    ``recv[dst]`` lists ``(src, t, [(local_expert, weight), ...])`` ordered by source rank, then token;
-    the hits keep the top-k slot order and carry ids local to ``dst``.
+    ``routes_per_rank[src][t]`` is the route of token t of rank src.  ``result[dst]`` lists
+    ``(src, t, [(expert local to dst, weight), ...])`` by source rank, then token; the hits keep their slot order.
     """
     world = len(routes_per_rank)
-    inbox: list[list] = [[] for _ in range(world)]
-    for src, routes in enumerate(routes_per_rank):
-        for t, route in enumerate(routes):
-            for dst in range(world):
-                lo = dst * experts_per_rank
-                hits = [(e - lo, w) for e, w in route if lo <= e < lo + experts_per_rank]
-                if hits:
-                    inbox[dst].append((src, t, hits))
-    return inbox
+    received = []
+    for dst in range(world):
+        first, beyond = dst * experts_per_rank, (dst + 1) * experts_per_rank
+        rows = []
+        for src in range(world):
+            for t, route in enumerate(routes_per_rank[src]):
+                here = [(expert - first, weight) for expert, weight in route if first <= expert < beyond]
+                if here:
+                    rows.append((src, t, here))
+        received.append(rows)
+    return received
