@@ -1,19 +1,22 @@
-"""Per-rank, communication-free stages of the variable-size ("naive") expert-parallel pipeline.
+"""The local stages of the variable-size ("naive") expert-parallel pipeline; nothing here communicates.
 
-Contract
-  * every rank owns the tokens of its own data-parallel shard;
-  * experts are placed in contiguous blocks: rank r owns experts ``[r*L, (r+1)*L)``;
-  * a token travels to a destination rank at most once, however many of its experts live there, and
-    carries K slots (local expert id or -1, routing weight or 0);
-  * send rows are ordered by destination rank, then by token index;
-  * the destination sums a row's local hits in slot order k = 0..K-1 in fp32 starting from +0.0 and
-    returns one partial row per received row;
-  * the source sums the partial rows of a token over destination ranks in ascending rank order, in
-    fp32 starting from +0.0.
+The rules these functions implement (and ``fixed.py`` must reproduce bit for bit on valid rows):
 
-This path needs the per-destination counts on the host, so it is not CUDA-graph capturable; it is
-the bitwise oracle of the fixed-capacity path on valid rows.  Behavioural counterpart of the
-reference's ``moeflow/dispatch.py:21-124``.
+placement    experts live in contiguous blocks, rank r owns ``[r * L, (r + 1) * L)``; tokens stay with the rank
+             of their data-parallel shard.
+one copy     a token is sent to a destination rank once, however many of its K experts live there.  The row
+             carries K slots: the expert id local to the destination (``INVALID`` where the slot belongs to
+             another rank) and the routing weight (0 there).
+send order   rows are grouped by destination rank; inside a group tokens are in ascending order.
+owner sum    the destination adds the (already weighted) expert outputs of a row's local slots in slot order
+             0..K-1, in fp32, starting from +0.0, and returns one partial row per received row.
+source sum   the source adds a token's partial rows in ascending destination-rank order, again fp32 from +0.0.
+
+A term that is absent is *skipped*, not added as zero: adding +0.0 would turn a -0.0 running sum into +0.0,
+and whatever sits in an absent slot must never be read as a number.
+
+Per-destination counts are needed on the host, so this pipeline cannot be captured in a CUDA graph.
+Behavioural counterpart of ``moeflow/dispatch.py:21-124`` of the reference (same names).
 """
 
 from __future__ import annotations
@@ -27,109 +30,110 @@ INVALID = -1
 
 @dataclass
 class DispatchPlan:
-    """Source-side plan; send row i goes to ``send_rank[i]`` and carries token ``send_token[i]``."""
-
-    send_token: torch.Tensor  # [S] int64
-    send_rank: torch.Tensor  # [S] int64, non-decreasing
-    send_counts: torch.Tensor  # [world] int64
-    slot_local_id: torch.Tensor  # [S, K] int32, INVALID where the slot lives elsewhere
-    slot_weight: torch.Tensor  # [S, K] fp32, 0 where INVALID
+    send_token: torch.Tensor     # [S] int64: the local token each send row carries
+    send_rank: torch.Tensor      # [S] int64: its destination rank (non-decreasing)
+    send_counts: torch.Tensor    # [world] int64: rows per destination
+    slot_local_id: torch.Tensor  # [S, K] int32: expert id local to the destination, INVALID elsewhere
+    slot_weight: torch.Tensor    # [S, K] fp32: routing weight, 0 where INVALID
 
 
-def plan_dispatch(
-    topk_ids: torch.Tensor, topk_weights: torch.Tensor, world: int, experts_per_rank: int
-) -> DispatchPlan:
-    n_tokens, _ = topk_ids.shape
-    ids = topk_ids.to(torch.int64)
-    owner = torch.div(ids, experts_per_rank, rounding_mode="floor")  # [T, K]
-    ranks = torch.arange(world, device=ids.device)
-    touches = (owner[:, None, :] == ranks[None, :, None]).any(dim=-1)  # [T, world]
-    # Enumerate (rank, token) pairs rank-major: transposing first makes nonzero() do the ordering.
-    rank_idx, token_idx = touches.transpose(0, 1).nonzero(as_tuple=True)
-    counts = touches.sum(dim=0).to(torch.int64)
+def plan_dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, world: int, experts_per_rank: int) -> DispatchPlan:
+    tokens, top_k = topk_ids.shape
+    expert = topk_ids.to(torch.int64)
+    owner = torch.div(expert, experts_per_rank, rounding_mode="floor")
+    # Every (token, slot) names a (destination, token) pair; numbering the pairs destination-major and keeping
+    # each number once gives the send rows already in their order.
+    token_of = torch.arange(tokens, device=expert.device)[:, None].expand(tokens, top_k)
+    pair = torch.unique(owner * max(tokens, 1) + token_of)  # sorted ascending
+    send_rank = torch.div(pair, max(tokens, 1), rounding_mode="floor")
+    send_token = pair - send_rank * max(tokens, 1)
+    send_counts = torch.bincount(send_rank, minlength=world)[:world].to(torch.int64)
 
-    here = owner[token_idx] == rank_idx[:, None]  # [S, K]
-    local = ids[token_idx] - rank_idx[:, None] * experts_per_rank
-    slot_local_id = torch.where(here, local, torch.full_like(local, INVALID)).to(torch.int32)
-    w = topk_weights.to(torch.float32)[token_idx]
-    slot_weight = torch.where(here, w, torch.zeros_like(w))
-    del n_tokens
-    return DispatchPlan(token_idx, rank_idx, counts, slot_local_id, slot_weight)
+    lives_there = owner[send_token] == send_rank[:, None]
+    local_id = (expert[send_token] - send_rank[:, None] * experts_per_rank).to(torch.int32)
+    weight = topk_weights.to(torch.float32)[send_token]
+    return DispatchPlan(
+        send_token=send_token,
+        send_rank=send_rank,
+        send_counts=send_counts,
+        slot_local_id=local_id.masked_fill(~lives_there, INVALID),
+        slot_weight=weight.masked_fill(~lives_there, 0.0),
+    )
 
 
 def pack_send(x: torch.Tensor, plan: DispatchPlan) -> torch.Tensor:
-    return x[plan.send_token]
+    """The hidden rows in send order."""
+    return x.index_select(0, plan.send_token)
 
 
 @dataclass
 class ExpertLayout:
-    """Destination-side expert-major order over the (received row, slot) entries."""
+    """Expert-major order of the live (received row, slot) entries on the destination."""
 
-    entry_row: torch.Tensor  # [N] int64
-    entry_slot: torch.Tensor  # [N] int64
-    expert_offsets: torch.Tensor  # [L + 1] int64; expert e owns entries [off[e], off[e+1])
+    entry_row: torch.Tensor       # [N] int64
+    entry_slot: torch.Tensor      # [N] int64
+    expert_offsets: torch.Tensor  # [L + 1] int64: local expert e owns entries [off[e], off[e + 1])
 
 
 def build_expert_layout(recv_local_id: torch.Tensor, num_local_experts: int) -> ExpertLayout:
-    _, top_k = recv_local_id.shape
-    flat = recv_local_id.reshape(-1).to(torch.int64)
-    live = torch.nonzero(flat != INVALID).reshape(-1)  # ascending (row, slot)
-    experts = flat[live]
-    # A stable sort keeps (row, slot) ascending inside every expert, so the layout is deterministic.
-    by_expert = torch.sort(experts, stable=True).indices
-    entries = live[by_expert]
-    counts = torch.bincount(experts, minlength=num_local_experts)
-    offsets = torch.zeros(num_local_experts + 1, dtype=torch.int64, device=flat.device)
-    torch.cumsum(counts, dim=0, out=offsets[1:])
-    return ExpertLayout(torch.div(entries, top_k, rounding_mode="floor"), entries % top_k, offsets)
+    rows, top_k = recv_local_id.shape
+    expert = recv_local_id.reshape(-1).to(torch.int64)
+    position = torch.arange(rows * top_k, device=expert.device)
+    live = expert != INVALID
+    # (expert, position) as one number: all keys differ, so a plain sort orders the entries by expert and,
+    # inside an expert, by (row, slot); this makes the layout unique without relying on sort stability.
+    ordered = torch.sort(expert[live] * max(rows * top_k, 1) + position[live]).values
+    ordered_expert = torch.div(ordered, max(rows * top_k, 1), rounding_mode="floor")
+    where = ordered - ordered_expert * max(rows * top_k, 1)
+    boundaries = torch.arange(num_local_experts + 1, device=expert.device)
+    return ExpertLayout(
+        entry_row=torch.div(where, top_k, rounding_mode="floor"),
+        entry_slot=where % top_k,
+        expert_offsets=torch.searchsorted(ordered_expert, boundaries),
+    )
 
 
 def gather_expert_input(recv_x: torch.Tensor, layout: ExpertLayout) -> torch.Tensor:
-    return recv_x[layout.entry_row]
+    """One input row per entry, in expert-major order."""
+    return recv_x.index_select(0, layout.entry_row)
 
 
 def entry_weights(layout: ExpertLayout, recv_weight: torch.Tensor) -> torch.Tensor:
-    """Routing weight of every expert-major entry, ``[N]`` fp32."""
+    """fp32 routing weight of every entry, in expert-major order."""
     return recv_weight.to(torch.float32)[layout.entry_row, layout.entry_slot]
 
 
 def _ordered_masked_sum(values: torch.Tensor, present: torch.Tensor) -> torch.Tensor:
-    """fp32 sum over dim 1 in index order, starting from +0.0, skipping absent terms.
-
-    ``values [N, S, H]``, ``present [N, S]``.  Skipped terms are not added at all (adding a zero could
-    turn a -0.0 running sum into +0.0, and garbage in absent slots must never be read as a number).
-    """
-    n, steps, width = values.shape
-    acc = torch.zeros(n, width, dtype=torch.float32, device=values.device)
-    for i in range(steps):
-        acc = torch.where(present[:, i, None], acc + values[:, i].to(torch.float32), acc)
-    return acc
+    """``values [N, S, H]``, ``present [N, S]`` -> fp32 ``[N, H]``: terms added in order s = 0..S-1 onto +0.0,
+    absent terms skipped."""
+    total = torch.zeros(values.shape[0], values.shape[2], dtype=torch.float32, device=values.device)
+    for term, there in zip(values.unbind(dim=1), present.unbind(dim=1)):
+        total = torch.where(there[:, None], total + term.to(torch.float32), total)
+    return total
 
 
-def reduce_local(
-    expert_out: torch.Tensor, layout: ExpertLayout, recv_weight: torch.Tensor, out_dtype: torch.dtype
-) -> torch.Tensor:
-    """Per received row: sum the local hits in slot order (fp32, from +0.0), cast to ``out_dtype``.
-
-    ``expert_out`` already holds ``bf16(weight * fp32 accumulator)``: the routing weight is applied in
-    the down-projection epilogue, only the sum happens here.
-    """
-    n_rows, top_k = recv_weight.shape
-    width = expert_out.shape[1]
-    slots = torch.zeros(n_rows, top_k, width, dtype=expert_out.dtype, device=expert_out.device)
-    present = torch.zeros(n_rows, top_k, dtype=torch.bool, device=expert_out.device)
-    slots[layout.entry_row, layout.entry_slot] = expert_out
-    present[layout.entry_row, layout.entry_slot] = True
-    return _ordered_masked_sum(slots, present).to(out_dtype)
+def _dense_terms(rows: int, steps: int, at_row: torch.Tensor, at_step: torch.Tensor, terms: torch.Tensor):
+    """Terms addressed by (row, step) laid out densely as ``[rows, steps, H]`` plus the mask of filled places.
+    The dense block is built by a gather through an index table, so unfilled places hold a copy of term 0 (or
+    nothing at all when there are no terms) and are masked out."""
+    table = torch.full((rows, steps), -1, dtype=torch.int64, device=terms.device)
+    table[at_row, at_step] = torch.arange(terms.shape[0], device=terms.device)
+    filled = table >= 0
+    if terms.shape[0] == 0:
+        return terms.new_zeros(rows, steps, terms.shape[1]), filled
+    return terms[table.clamp(min=0)], filled
 
 
-def combine(
-    partials: torch.Tensor, plan: DispatchPlan, num_tokens: int, world: int, out_dtype: torch.dtype
-) -> torch.Tensor:
-    """Per owned token: sum the returned partial rows in ascending destination-rank order."""
-    width = partials.shape[1]
-    by_rank = torch.zeros(num_tokens, world, width, dtype=torch.float32, device=partials.device)
-    present = torch.zeros(num_tokens, world, dtype=torch.bool, device=partials.device)
-    by_rank[plan.send_token, plan.send_rank] = partials.to(torch.float32)
-    present[plan.send_token, plan.send_rank] = True
-    return _ordered_masked_sum(by_rank, present).to(out_dtype)
+def reduce_local(expert_out: torch.Tensor, layout: ExpertLayout, recv_weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """One partial row per received row.  ``expert_out`` is in expert-major order and already carries the
+    routing weight (it is applied to the fp32 accumulator of the down projection, before the single cast), so
+    ``recv_weight`` only supplies the shape here."""
+    rows, top_k = recv_weight.shape
+    terms, filled = _dense_terms(rows, top_k, layout.entry_row, layout.entry_slot, expert_out)
+    return _ordered_masked_sum(terms, filled).to(out_dtype)
+
+
+def combine(partials: torch.Tensor, plan: DispatchPlan, num_tokens: int, world: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """The final rows of this rank's tokens from the partial rows that came back (in send order)."""
+    terms, filled = _dense_terms(num_tokens, world, plan.send_token, plan.send_rank, partials)
+    return _ordered_masked_sum(terms, filled).to(out_dtype)
