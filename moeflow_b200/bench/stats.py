@@ -8,7 +8,6 @@ own standard deviations.  Counterpart of the reference's ``scripts/bench/stats.p
 from __future__ import annotations
 
 import math
-import statistics
 from dataclasses import asdict, dataclass
 
 
@@ -68,15 +67,40 @@ def t95(df: int) -> float:
     return 0.5 * (lo + hi)
 
 
+class Sample:
+    """Order statistics and moments of a list of measurements (values kept sorted)."""
+
+    def __init__(self, values):
+        self.sorted = sorted(float(v) for v in values)
+        if not self.sorted:
+            raise ValueError("empty sample")
+
+    def __len__(self) -> int:
+        return len(self.sorted)
+
+    def quantile(self, q: float) -> float:
+        """Linear interpolation between the two nearest order statistics, ``q`` in [0, 100]."""
+        rank = (len(self) - 1) * (q / 100.0)
+        floor = min(int(rank), len(self) - 1)
+        ceil = min(floor + 1, len(self) - 1)
+        lower, upper = self.sorted[floor], self.sorted[ceil]
+        return lower + (upper - lower) * (rank - floor)
+
+    @property
+    def mean(self) -> float:
+        return math.fsum(self.sorted) / len(self)
+
+    @property
+    def std(self) -> float:
+        """Sample standard deviation (n - 1 in the denominator); 0 for a single value."""
+        if len(self) < 2:
+            return 0.0
+        centre = self.mean
+        return math.sqrt(math.fsum((v - centre) ** 2 for v in self.sorted) / (len(self) - 1))
+
+
 def percentile(xs: list[float], q: float) -> float:
-    """Percentile with linear interpolation between order statistics, ``q`` in [0, 100]."""
-    if not xs:
-        raise ValueError("empty sample")
-    ordered = sorted(xs)
-    where = (len(ordered) - 1) * q / 100.0
-    below = int(math.floor(where))
-    above = min(below + 1, len(ordered) - 1)
-    return ordered[below] + (ordered[above] - ordered[below]) * (where - below)
+    return Sample(xs).quantile(q)
 
 
 @dataclass
@@ -94,47 +118,38 @@ class Summary:
 
 
 def summarize(xs: list[float]) -> Summary:
-    return Summary(
-        n=len(xs),
-        median=statistics.median(xs),
-        p95=percentile(xs, 95.0),
-        mean=statistics.fmean(xs),
-        std=statistics.stdev(xs) if len(xs) > 1 else 0.0,
-        min=min(xs),
-        max=max(xs),
-    )
+    s = Sample(xs)
+    return Summary(n=len(s), median=s.quantile(50.0), p95=s.quantile(95.0), mean=s.mean, std=s.std,
+                   min=s.sorted[0], max=s.sorted[-1])
 
 
 @dataclass
 class PairedResult:
     n: int
-    mean_diff: float  # mean(b - a); negative means B is faster
-    ci95: tuple[float, float]
-    median_improvement: float  # median(a) - median(b)
-    pooled_std: float  # the larger of the two arms' standard deviations
-    significant: bool
+    mean_diff: float           # mean of b[i] - a[i]; negative when B is the faster arm
+    ci95: tuple[float, float]  # 95 % confidence interval of that mean (Student t, n - 1 degrees of freedom)
+    median_improvement: float  # median(a) - median(b); positive when B is the faster arm
+    pooled_std: float          # the noisier arm's own standard deviation
+    significant: bool          # both conditions of the rule hold
 
     @property
     def beneficial(self) -> bool:
-        return self.significant and self.median_improvement > 0
+        return self.significant and self.median_improvement > 0.0
 
     def to_dict(self) -> dict:
-        d = asdict(self)
-        d["ci95"] = list(self.ci95)
-        d["beneficial"] = self.beneficial
-        return d
+        return {**asdict(self), "ci95": list(self.ci95), "beneficial": self.beneficial}
 
 
 def paired_ab(a: list[float], b: list[float]) -> PairedResult:
-    """Paired comparison of alternating repetitions (``a[i]`` and ``b[i]`` measured back to back)."""
+    """Decision for two arms measured in alternation (``a[i]`` and ``b[i]`` back to back)."""
     if len(a) != len(b) or len(a) < 2:
         raise ValueError("need equal-length samples with n >= 2")
-    diffs = [after - before for before, after in zip(a, b)]
-    n = len(diffs)
-    mean_diff = statistics.fmean(diffs)
-    half_width = t95(n - 1) * statistics.stdev(diffs) / math.sqrt(n)
-    ci = (mean_diff - half_width, mean_diff + half_width)
-    gain = statistics.median(a) - statistics.median(b)
-    noise = max(statistics.stdev(a), statistics.stdev(b))
-    excludes_zero = ci[0] > 0.0 or ci[1] < 0.0
-    return PairedResult(n, mean_diff, ci, gain, noise, excludes_zero and abs(gain) > noise)
+    arm_a, arm_b = Sample(a), Sample(b)
+    change = Sample(after - before for before, after in zip(a, b))
+    reach = t95(len(change) - 1) * change.std / math.sqrt(len(change))
+    interval = (change.mean - reach, change.mean + reach)
+    gain = arm_a.quantile(50.0) - arm_b.quantile(50.0)
+    noise = max(arm_a.std, arm_b.std)
+    clear_of_zero = interval[0] > 0.0 or interval[1] < 0.0
+    return PairedResult(n=len(change), mean_diff=change.mean, ci95=interval, median_improvement=gain,
+                        pooled_std=noise, significant=clear_of_zero and abs(gain) > noise)
