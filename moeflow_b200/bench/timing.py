@@ -1,10 +1,17 @@
-"""Multi-rank latency measurement: barrier-aligned start, device-side timing, slowest rank wins.
+"""Latency of a multi-rank step, measured on the device.
 
-Each repetition: barrier on all ranks -> CUDA events around ``inner`` back-to-back calls -> per-rank
-mean per call -> ``all_reduce(MAX)``.  Graph mode captures ``inner`` calls into one CUDA graph once
-and replays it per repetition; a function that cannot be captured is reported as such, never timed
-eagerly behind the caller's back.  Optionally an L2 flush (a write larger than L2) precedes every
-repetition, outside the timed interval.  Counterpart of ``scripts/bench/timing.py:27-127``.
+One *sample* is taken like this (``Stopwatch.sample``): optionally flush L2 (a write larger than the cache, so
+the step starts from HBM), line all ranks up at a barrier and drain the device, record a CUDA event, run the
+work (``inner`` back-to-back calls, or one replay of a graph that holds them), record the second event, wait
+for it, divide by ``inner`` and take the MAX over the ranks: the slowest rank is the step time.  The flush and
+the barrier are outside the timed interval.
+
+``time_eager`` calls the function; ``time_graph`` captures ``inner`` calls into one CUDA graph and replays it.
+A function that cannot be captured is reported as such (``capturable=False`` with the error text) and is never
+silently timed eagerly.  ``time_graphs_alternating`` replays two captured variants A, B, A, B, ... so that
+their samples pair up by index for the paired A/B rule.  Graphs are always released before returning, since a
+live graph that holds communicator work must not outlive the process group.
+Counterpart of ``scripts/bench/timing.py:27-127`` of the reference.
 """
 
 from __future__ import annotations
@@ -18,33 +25,34 @@ import torch.distributed as dist
 
 @dataclass
 class TimingResult:
-    mode: str
-    per_call_us: list[float] = field(default_factory=list)  # one sample per repetition, max over ranks
+    mode: str                                                 # "eager" | "graph"
+    per_call_us: list[float] = field(default_factory=list)    # one value per repetition, max over ranks
     inner: int = 1
     capturable: bool = True
     error: str | None = None
 
 
-def _dist_on() -> bool:
+def _in_a_group() -> bool:
     return dist.is_available() and dist.is_initialized()
 
 
 def max_over_ranks(value: float, group=None) -> float:
-    if not _dist_on():
+    if not _in_a_group():
         return value
-    t = torch.tensor([value], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-    return float(t.item())
+    box = torch.full((1,), value, dtype=torch.float64, device="cuda")
+    dist.all_reduce(box, op=dist.ReduceOp.MAX, group=group)
+    return float(box[0])
 
 
 def aligned_start(group=None) -> None:
-    if _dist_on():
+    """All ranks at the same point, nothing pending on this device."""
+    if _in_a_group():
         dist.barrier(group=group, device_ids=[torch.cuda.current_device()])
     torch.cuda.synchronize()
 
 
 class L2Flush:
-    """Writes a buffer larger than the 126 MB L2 so that the next kernel starts from HBM."""
+    """Overwrites a buffer larger than the 126 MB L2; whatever ran before is evicted."""
 
     def __init__(self, nbytes: int = 256 << 20, device=None):
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device or "cuda")
@@ -53,42 +61,54 @@ class L2Flush:
         self.buf.zero_()
 
 
-def _one_sample(run: Callable[[], None], inner: int, group, flush) -> float:
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if flush is not None:
-        flush()
-    aligned_start(group)
-    start.record()
-    run()
-    end.record()
-    end.synchronize()
-    return max_over_ranks(start.elapsed_time(end) * 1e3 / inner, group)
+class Stopwatch:
+    """Takes samples of one piece of work under fixed conditions (group, flush, calls per sample)."""
+
+    def __init__(self, inner: int, group=None, flush: Callable[[], None] | None = None):
+        self.inner, self.group, self.flush = inner, group, flush
+        self.begin = torch.cuda.Event(enable_timing=True)
+        self.finish = torch.cuda.Event(enable_timing=True)
+
+    def sample(self, work: Callable[[], None]) -> float:
+        """Microseconds per call, slowest rank."""
+        if self.flush is not None:
+            self.flush()
+        aligned_start(self.group)
+        self.begin.record()
+        work()
+        self.finish.record()
+        self.finish.synchronize()
+        return max_over_ranks(self.begin.elapsed_time(self.finish) * 1000.0 / self.inner, self.group)
+
+    def samples(self, work: Callable[[], None], count: int) -> list[float]:
+        return [self.sample(work) for _ in range(count)]
+
+
+def _repeat(fn: Callable[[], object], times: int) -> Callable[[], None]:
+    def run() -> None:
+        for _ in range(times):
+            fn()
+
+    return run
 
 
 def time_eager(fn, reps: int = 10, inner: int = 20, warmup: int = 5, group=None, flush=None) -> TimingResult:
-    for _ in range(warmup):
-        fn()
-
-    def run():
-        for _ in range(inner):
-            fn()
-
-    return TimingResult("eager", [_one_sample(run, inner, group, flush) for _ in range(reps)], inner)
+    _repeat(fn, warmup)()
+    return TimingResult("eager", Stopwatch(inner, group, flush).samples(_repeat(fn, inner), reps), inner)
 
 
 def capture(fn, warmup: int = 3, inner: int = 1, group=None) -> torch.cuda.CUDAGraph:
-    """Capture ``inner`` back-to-back calls (raises when the function cannot be captured)."""
+    """``inner`` back-to-back calls as one CUDA graph, after ``warmup`` calls on a side stream (lazy
+    initialisation must not happen during capture).  Raises whatever the capture raises."""
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        for _ in range(warmup):
-            fn()
+        _repeat(fn, warmup)()
     torch.cuda.current_stream().wait_stream(side)
     aligned_start(group)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        for _ in range(inner):
-            fn()
+        _repeat(fn, inner)()
     aligned_start(group)
     return graph
 
@@ -96,26 +116,27 @@ def capture(fn, warmup: int = 3, inner: int = 1, group=None) -> torch.cuda.CUDAG
 def time_graph(fn, reps: int = 10, inner: int = 20, warmup: int = 3, group=None, flush=None) -> TimingResult:
     try:
         graph = capture(fn, warmup, inner, group)
-    except Exception as exc:  # "not capturable" is a result of its own
+    except Exception as problem:  # not being capturable is a finding, not a crash
         torch.cuda.synchronize()
-        return TimingResult("graph", [], inner, capturable=False, error=f"{type(exc).__name__}: {exc}"[:500])
-    graph.replay()
-    samples = [_one_sample(graph.replay, inner, group, flush) for _ in range(reps)]
-    del graph  # graphs must go before the process group does
+        return TimingResult("graph", [], inner, capturable=False, error=f"{type(problem).__name__}: {problem}"[:500])
+    graph.replay()  # one untimed replay
+    result = TimingResult("graph", Stopwatch(inner, group, flush).samples(graph.replay, reps), inner)
+    del graph
     torch.cuda.synchronize()
-    return TimingResult("graph", samples, inner)
+    return result
 
 
 def time_graphs_alternating(fn_a, fn_b, reps: int = 10, inner: int = 20, group=None, flush=None):
-    """A/B timing: both variants captured, then replayed A, B, A, B, ...; samples are paired by index."""
-    graph_a = capture(fn_a, inner=inner, group=group)
-    graph_b = capture(fn_b, inner=inner, group=group)
-    graph_a.replay()
-    graph_b.replay()
-    a, b = [], []
+    """``(samples of A, samples of B)``, taken in the order A, B, A, B, ..."""
+    graphs = [capture(fn, inner=inner, group=group) for fn in (fn_a, fn_b)]
+    for graph in graphs:
+        graph.replay()
+    watch = Stopwatch(inner, group, flush)
+    taken: tuple[list[float], list[float]] = ([], [])
     for _ in range(reps):
-        a.append(_one_sample(graph_a.replay, inner, group, flush))
-        b.append(_one_sample(graph_b.replay, inner, group, flush))
-    del graph_a, graph_b
+        for arm, graph in zip(taken, graphs):
+            arm.append(watch.sample(graph.replay))
+    del graph
+    graphs.clear()
     torch.cuda.synchronize()
-    return a, b
+    return taken

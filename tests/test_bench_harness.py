@@ -176,3 +176,105 @@ def test_weight_source_specs_and_profiler_window():
     assert w13.shape == (2, 16, 16) and w2.shape == (2, 16, 8) and bias.shape == (4,)
     with profile_layer("nothing to record", enabled=False) as window:
         assert not window.active
+
+
+class _FakeCuda:
+    """Enough of ``torch.cuda`` to run the timing helpers on a machine without a GPU: events read a counter
+    that every "kernel" advances by one millisecond, graphs record the calls made during capture."""
+
+    def __init__(self):
+        self.clock_ms = 0.0
+        self.log = []
+        outer = self
+
+        class Event:
+            def __init__(self, enable_timing=False):
+                self.at = None
+
+            def record(self):
+                self.at = outer.clock_ms
+
+            def synchronize(self):
+                pass
+
+            def elapsed_time(self, other):
+                return other.at - self.at
+
+        class Stream:
+            def wait_stream(self, other):
+                pass
+
+        class Graph:
+            def __init__(self):
+                self.calls = []
+
+            def replay(self):
+                for fn in self.calls:
+                    fn()
+
+        self.Event, self.Stream, self.CUDAGraph = Event, Stream, Graph
+        self._capturing = None
+
+    def synchronize(self):
+        self.log.append("sync")
+
+    def current_stream(self):
+        return self.Stream()
+
+    def stream(self, s):
+        import contextlib
+
+        return contextlib.nullcontext()
+
+    def graph(self, g):
+        import contextlib
+
+        outer = self
+
+        @contextlib.contextmanager
+        def capturing():
+            outer._capturing = g
+            try:
+                yield
+            finally:
+                outer._capturing = None
+
+        return capturing()
+
+    def kernel(self, tag):
+        """A stand-in workload: runs now, or is recorded when a capture is open."""
+        def body():
+            self.clock_ms += 1.0
+            self.log.append(tag)
+
+        if self._capturing is not None:
+            self._capturing.calls.append(body)
+        else:
+            body()
+
+
+def test_timing_helpers_on_a_fake_device(monkeypatch):
+    from moeflow_b200.bench import timing
+
+    fake = _FakeCuda()
+    for name in ("Event", "Stream", "CUDAGraph", "synchronize", "current_stream", "stream", "graph"):
+        monkeypatch.setattr(torch.cuda, name, getattr(fake, name))
+    flushes = []
+    eager = timing.time_eager(lambda: fake.kernel("e"), reps=3, inner=4, warmup=2, flush=lambda: flushes.append(1))
+    assert eager.mode == "eager" and eager.per_call_us == [1000.0] * 3 and len(flushes) == 3
+    assert fake.log.count("e") == 2 + 3 * 4
+
+    graphed = timing.time_graph(lambda: fake.kernel("g"), reps=2, inner=5, warmup=1)
+    assert graphed.capturable and graphed.per_call_us == [1000.0, 1000.0]
+    assert fake.log.count("g") == 1 + 5 * (1 + 2)  # warm-up call, one untimed replay, two timed replays
+
+    def refuses():
+        raise RuntimeError("operation not permitted when stream is capturing")
+
+    failed = timing.time_graph(refuses, reps=2, inner=2, warmup=0)
+    assert not failed.capturable and failed.per_call_us == [] and "not permitted" in failed.error
+
+    a, b = timing.time_graphs_alternating(lambda: fake.kernel("A"), lambda: (fake.kernel("B"), fake.kernel("B")), reps=3, inner=1)
+    assert a == [1000.0] * 3 and b == [2000.0] * 3
+    order = [t for t in fake.log if t in "AB"]
+    assert order[-9:] == ["A", "B", "B"] * 3  # strictly alternating
