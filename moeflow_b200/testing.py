@@ -44,12 +44,15 @@ def make_weights(cfg: MoEConfig, seed: int, device="cpu", dtype=torch.bfloat16, 
     if experts is None:
         w13, w2 = _gate_up_and_down(cfg, cfg.n_routed_experts, _generator(seed))
         return w13.to(device=device, dtype=dtype), w2.to(device=device, dtype=dtype)
-    blocks = [_gate_up_and_down(cfg, 1, _generator(seed * 1_000_003 + e)) for e in experts]
-    stack = lambda which: torch.cat([b[which] for b in blocks]).to(device=device, dtype=dtype)  # noqa: E731
-    if not blocks:
+    if len(experts) == 0:
         empty13, empty2 = _gate_up_and_down(cfg, 0, _generator(seed))
         return empty13.to(device=device, dtype=dtype), empty2.to(device=device, dtype=dtype)
-    return stack(0), stack(1)
+    gate_up, down = [], []
+    for e in experts:  # converted one expert at a time, so the fp32 draw of a large shard never exists whole
+        w13, w2 = _gate_up_and_down(cfg, 1, _generator(seed * 1_000_003 + e))
+        gate_up.append(w13.to(device=device, dtype=dtype))
+        down.append(w2.to(device=device, dtype=dtype))
+    return torch.cat(gate_up), torch.cat(down)
 
 
 def make_hidden(num_tokens: int, cfg: MoEConfig, seed: int, device="cpu", dtype=torch.bfloat16):
