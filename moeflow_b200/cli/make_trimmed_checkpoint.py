@@ -1,11 +1,17 @@
-"""Cut a checkpoint down to its first N decoder layers (width unchanged).
+"""A shallower copy of a checkpoint: the first N decoder layers at full width.
 
     python -m moeflow_b200.cli.make_trimmed_checkpoint --src <snapshot> --dst <dir> --num-layers 4
 
-Keeps decoder layers ``[0, N)`` and everything that is not a decoder layer (embeddings, final norm,
-lm_head, vision tower); drops the other layers and the multi-token-prediction layer; trims the
-per-layer lists of the config; links tokenizer/processor files instead of copying them.
-Counterpart of ``scripts/make_trimmed_checkpoint.py:21-77``.
+Serving experiments that only need "a model of the right layer shape" load in seconds from such a copy.
+What is kept: decoder layers ``0 .. N-1`` and every tensor that does not belong to a decoder layer
+(embeddings, final norm, output head, vision tower).  What goes: the deeper layers and the multi-token-
+prediction layer.  The configuration is cut to match (layer count, per-layer type lists, the layer-index
+lists of the linear-attention block), the kept tensors are re-packed shard by shard and re-indexed, and the
+tokenizer / processor files are linked rather than copied.  A ``TRIMMED_FROM.json`` records the origin.
+
+The work is planned first (``plan_shards``: which tensors of which source shard survive) and then carried
+out, so the plan can be inspected or tested without touching tensor data.
+Same result as ``scripts/make_trimmed_checkpoint.py:21-77`` of the reference.
 """
 
 from __future__ import annotations
@@ -16,73 +22,94 @@ import os
 import re
 from pathlib import Path
 
-LAYER_NAME = re.compile(r"^model\.language_model\.layers\.(\d+)\.")
-PER_LAYER_LISTS = ("layer_types", "indexer_types", "mlp_layer_types")
-LAYER_INDEX_LISTS = ("kda_layers", "full_attn_layers")
+INDEX_FILE = "model.safetensors.index.json"
+CONFIG_FILE = "config.json"
+_DECODER_LAYER = re.compile(r"model\.language_model\.layers\.(?P<layer>\d+)\.")
+_LISTS_WITH_ONE_ENTRY_PER_LAYER = ("layer_types", "indexer_types", "mlp_layer_types")
+_LISTS_OF_LAYER_INDICES = ("kda_layers", "full_attn_layers")  # inside linear_attn_config
 
 
-def keeps(name: str, num_layers: int) -> bool:
-    m = LAYER_NAME.match(name)
-    return m is None or int(m.group(1)) < num_layers
+def layer_of(tensor_name: str) -> int | None:
+    """Decoder layer a tensor belongs to, or ``None`` for tensors outside the decoder stack."""
+    found = _DECODER_LAYER.match(tensor_name)
+    return int(found["layer"]) if found else None
+
+
+def keeps(tensor_name: str, num_layers: int) -> bool:
+    layer = layer_of(tensor_name)
+    return layer is None or layer < num_layers
 
 
 def trim_config(cfg: dict, num_layers: int) -> dict:
-    text = cfg.get("text_config", cfg)
-    if num_layers > text["num_hidden_layers"]:
-        raise ValueError(f"checkpoint has only {text['num_hidden_layers']} layers")
-    text["num_hidden_layers"] = num_layers
-    text["num_nextn_predict_layers"] = 0
-    for key in PER_LAYER_LISTS:
+    """Cut the (text) configuration to ``num_layers`` layers, in place; returns ``cfg``."""
+    text = cfg["text_config"] if "text_config" in cfg else cfg
+    depth = text["num_hidden_layers"]
+    if not 0 < num_layers <= depth:
+        raise ValueError(f"cannot keep {num_layers} layers of a checkpoint with {depth}")
+    text.update(num_hidden_layers=num_layers, num_nextn_predict_layers=0)
+    for key in _LISTS_WITH_ONE_ENTRY_PER_LAYER:
         if isinstance(text.get(key), list):
-            text[key] = text[key][:num_layers]
-    linear = text.get("linear_attn_config") or {}
-    for key in LAYER_INDEX_LISTS:
-        if key in linear:
-            linear[key] = [i for i in linear[key] if i < num_layers]
+            del text[key][num_layers:]
+    linear_attention = text.get("linear_attn_config")
+    if isinstance(linear_attention, dict):
+        for key in _LISTS_OF_LAYER_INDICES:
+            if key in linear_attention:
+                linear_attention[key] = [layer for layer in linear_attention[key] if layer < num_layers]
     return cfg
 
 
-def trim(src: Path, dst: Path, num_layers: int, verbose: bool = True) -> None:
+def plan_shards(weight_map: dict[str, str], num_layers: int) -> list[tuple[str, str, list[str]]]:
+    """``[(source shard, new shard name, surviving tensor names)]``; source shards with nothing left are
+    dropped and the new shards are numbered from 1 in source-name order."""
+    survivors: dict[str, list[str]] = {}
+    for tensor_name, shard in weight_map.items():
+        if keeps(tensor_name, num_layers):
+            survivors.setdefault(shard, []).append(tensor_name)
+    return [(shard, f"model-{number:05d}.safetensors", survivors[shard])
+            for number, shard in enumerate(sorted(survivors), start=1)]
+
+
+def _repack(src: Path, dst: Path, plan, say) -> dict[str, str]:
     from safetensors import safe_open
     from safetensors.torch import save_file
 
+    where: dict[str, str] = {}
+    for old_shard, new_shard, names in plan:
+        with safe_open(src / old_shard, framework="pt") as reader:
+            kept = {name: reader.get_tensor(name) for name in names}
+        save_file(kept, dst / new_shard, metadata={"format": "pt"})
+        where.update((name, new_shard) for name in names)
+        say(f"{old_shard} -> {new_shard}: {len(names)} tensors")
+    return where
+
+
+def _link_everything_else(src: Path, dst: Path) -> None:
+    for entry in src.iterdir():
+        is_model_data = entry.suffix == ".safetensors" or entry.name in (CONFIG_FILE, INDEX_FILE)
+        if not is_model_data and not (dst / entry.name).exists():
+            os.symlink(entry.resolve(), dst / entry.name)
+
+
+def trim(src: Path, dst: Path, num_layers: int, verbose: bool = True) -> None:
+    src, dst = Path(src), Path(dst)
+    say = (lambda line: print(line, flush=True)) if verbose else (lambda line: None)
+    config = trim_config(json.loads((src / CONFIG_FILE).read_text()), num_layers)  # validates before anything is written
+    plan = plan_shards(json.loads((src / INDEX_FILE).read_text())["weight_map"], num_layers)
     dst.mkdir(parents=True, exist_ok=True)
-    cfg = trim_config(json.loads((src / "config.json").read_text()), num_layers)
-    (dst / "config.json").write_text(json.dumps(cfg, indent=2))
-
-    weight_map = json.loads((src / "model.safetensors.index.json").read_text())["weight_map"]
-    per_shard: dict[str, list[str]] = {}
-    for name, shard in weight_map.items():
-        if keeps(name, num_layers):
-            per_shard.setdefault(shard, []).append(name)
-    new_map: dict[str, str] = {}
-    for i, shard in enumerate(sorted(per_shard), start=1):
-        with safe_open(src / shard, framework="pt") as handle:
-            tensors = {name: handle.get_tensor(name) for name in per_shard[shard]}
-        out_name = f"model-{i:05d}.safetensors"
-        save_file(tensors, dst / out_name, metadata={"format": "pt"})
-        new_map.update(dict.fromkeys(tensors, out_name))
-        if verbose:
-            print(f"{shard} -> {out_name}: {len(tensors)} tensors", flush=True)
-    (dst / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": new_map}, indent=1))
-
-    skip = {"config.json", "model.safetensors.index.json"}
-    for p in src.iterdir():
-        if p.suffix == ".safetensors" or p.name in skip:
-            continue
-        link = dst / p.name
-        if not link.exists():
-            os.symlink(p.resolve(), link)
+    (dst / CONFIG_FILE).write_text(json.dumps(config, indent=2))
+    new_map = _repack(src, dst, plan, say)
+    (dst / INDEX_FILE).write_text(json.dumps({"metadata": {}, "weight_map": new_map}, indent=1))
+    _link_everything_else(src, dst)
     (dst / "TRIMMED_FROM.json").write_text(json.dumps({"src": str(src), "num_layers": num_layers}, indent=1))
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--src", required=True)
-    ap.add_argument("--dst", required=True)
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--src", required=True, type=Path, help="checkpoint directory (config, index, shards)")
+    ap.add_argument("--dst", required=True, type=Path, help="directory to create")
     ap.add_argument("--num-layers", type=int, default=4)
-    args = ap.parse_args()
-    trim(Path(args.src), Path(args.dst), args.num_layers)
+    args = ap.parse_args(argv)
+    trim(args.src, args.dst, args.num_layers)
 
 
 if __name__ == "__main__":

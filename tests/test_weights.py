@@ -2,6 +2,7 @@
 
 import json
 
+import pytest
 import torch
 from safetensors import safe_open
 from safetensors.torch import save_file
@@ -98,3 +99,21 @@ def test_trimmed_checkpoint(tmp_path):
     with safe_open(dst / "model-00001.safetensors", framework="pt") as h:
         assert h.get_tensor("model.language_model.layers.3.mlp.gate.weight")[0, 0] == 3.0
     assert json.loads((dst / "TRIMMED_FROM.json").read_text())["num_layers"] == 4
+
+
+def test_trim_plan_and_config_rules():
+    from moeflow_b200.cli.make_trimmed_checkpoint import keeps, layer_of, plan_shards, trim_config
+
+    assert layer_of("model.language_model.layers.12.mlp.gate.weight") == 12 and layer_of("lm_head.weight") is None
+    assert keeps("model.visual.blocks.30.attn.qkv.weight", 2)  # a vision block is not a decoder layer
+    weight_map = {"model.language_model.layers.0.a": "s2", "model.language_model.layers.9.a": "s1", "lm_head.weight": "s3",
+                  "model.language_model.layers.1.a": "s2"}
+    assert plan_shards(weight_map, 2) == [
+        ("s2", "model-00001.safetensors", ["model.language_model.layers.0.a", "model.language_model.layers.1.a"]),
+        ("s3", "model-00002.safetensors", ["lm_head.weight"]),
+    ]
+    flat = trim_config({"num_hidden_layers": 3, "layer_types": ["x", "y", "z"]}, 2)  # no nested text_config
+    assert flat == {"num_hidden_layers": 2, "num_nextn_predict_layers": 0, "layer_types": ["x", "y"]}
+    for bad in (0, 4):
+        with pytest.raises(ValueError):
+            trim_config({"num_hidden_layers": 3}, bad)
