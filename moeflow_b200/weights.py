@@ -58,79 +58,75 @@ def quant_block_fp8(w: torch.Tensor, block: tuple[int, int] = (128, 128)) -> tup
 
 
 class CheckpointReader:
+    """Reads tensors by name through the shard index, and a layer's experts in the two layouts above."""
+
     def __init__(self, snapshot: str | Path = DEFAULT_SNAPSHOT):
         self.root = Path(snapshot)
         self.index: dict[str, str] = json.loads((self.root / "model.safetensors.index.json").read_text())["weight_map"]
-        cfg = json.loads((self.root / "config.json").read_text())
-        quant = cfg.get("quantization_config") or {}
-        self.block: tuple[int, int] = tuple(quant.get("weight_block_size", (128, 128)))  # type: ignore[assignment]
+        quant = json.loads((self.root / "config.json").read_text()).get("quantization_config") or {}
+        rows, cols = quant.get("weight_block_size", (128, 128))
+        self.block: tuple[int, int] = (int(rows), int(cols))
 
+    # ---- raw access ------------------------------------------------------------------------------------
     def get(self, names: list[str]) -> dict[str, torch.Tensor]:
-        """Read the named tensors, opening every shard file once."""
+        """The named tensors; every shard file that holds one of them is opened once."""
         from safetensors import safe_open
 
-        wanted: dict[str, list[str]] = {}
+        by_shard: dict[str, list[str]] = {}
         for name in names:
-            wanted.setdefault(self.index[name], []).append(name)
-        out: dict[str, torch.Tensor] = {}
-        for shard, shard_names in wanted.items():
+            by_shard.setdefault(self.index[name], []).append(name)
+        found: dict[str, torch.Tensor] = {}
+        for shard, wanted in by_shard.items():
             with safe_open(self.root / shard, framework="pt") as handle:
-                for name in shard_names:
-                    out[name] = handle.get_tensor(name)
-        return out
+                found.update((name, handle.get_tensor(name)) for name in wanted)
+        return found
 
-    def _expert_names(self, layer: int, experts: range) -> list[str]:
-        base = PREFIX.format(layer=layer)
-        names = []
+    def _projections(self, layer: int, experts: range):
+        """For every requested expert: ``{projection: (weight as stored, block scales or None)}``."""
+        stem = PREFIX.format(layer=layer) + ".experts.{expert}.{projection}"
+        weight_of = {(e, p): stem.format(expert=e, projection=p) + ".weight" for e in experts for p in PROJECTIONS}
+        scale_of = {key: name + "_scale_inv" for key, name in weight_of.items() if name + "_scale_inv" in self.index}
+        raw = self.get([*weight_of.values(), *scale_of.values()])
         for e in experts:
-            for proj in PROJECTIONS:
-                stem = f"{base}.experts.{e}.{proj}"
-                names.append(f"{stem}.weight")
-                if f"{stem}.weight_scale_inv" in self.index:
-                    names.append(f"{stem}.weight_scale_inv")
-        return names
+            yield {p: (raw[weight_of[e, p]], raw[scale_of[e, p]] if (e, p) in scale_of else None) for p in PROJECTIONS}
 
-    def _dense(self, stem: str, raw: dict[str, torch.Tensor]) -> torch.Tensor:
-        w = raw[f"{stem}.weight"]
-        if w.dtype == torch.float8_e4m3fn:
-            return dequant_block_fp8(w, raw[f"{stem}.weight_scale_inv"], self.block)
-        return w.to(torch.float32)
+    def _as_fp32(self, weight: torch.Tensor, scales: torch.Tensor | None) -> torch.Tensor:
+        if weight.dtype == torch.float8_e4m3fn:
+            return dequant_block_fp8(weight, scales, self.block)
+        return weight.to(torch.float32)
 
+    # ---- a layer's experts ---------------------------------------------------------------------------------
     def expert_weights(self, layer: int, experts: range, dtype=torch.bfloat16) -> tuple[torch.Tensor, torch.Tensor]:
-        raw = self.get(self._expert_names(layer, experts))
-        base = PREFIX.format(layer=layer)
-        w13, w2 = [], []
-        for e in experts:
-            stem = f"{base}.experts.{e}"
-            gate, up = self._dense(f"{stem}.gate_proj", raw), self._dense(f"{stem}.up_proj", raw)
-            w13.append(torch.cat([gate, up], dim=0).to(dtype))
-            w2.append(self._dense(f"{stem}.down_proj", raw).to(dtype))
-        return torch.stack(w13), torch.stack(w2)
+        """Dequantised: ``w13 [n, 2I, H]`` (gate rows, then up rows) and ``w2 [n, H, I]`` in ``dtype``."""
+        gate_up, down = [], []
+        for projections in self._projections(layer, experts):
+            dense = {name: self._as_fp32(*stored) for name, stored in projections.items()}
+            gate_up.append(torch.cat((dense["gate_proj"], dense["up_proj"])).to(dtype))
+            down.append(dense["down_proj"].to(dtype))
+        return torch.stack(gate_up), torch.stack(down)
 
     def expert_weights_fp8(self, layer: int, experts: range):
-        """Keep e4m3 weights and their fp32 128x128 block scales un-dequantised."""
-        raw = self.get(self._expert_names(layer, experts))
-        base = PREFIX.format(layer=layer)
-        q13, s13, q2, s2 = [], [], [], []
-        for e in experts:
-            stem = f"{base}.experts.{e}"
-            parts = {}
-            for proj in PROJECTIONS:
-                w = raw[f"{stem}.{proj}.weight"]
-                if w.dtype != torch.float8_e4m3fn:
-                    raise ValueError(f"{stem}.{proj} is {w.dtype}, not float8_e4m3fn")
-                parts[proj] = (w, raw[f"{stem}.{proj}.weight_scale_inv"].to(torch.float32))
-            if parts["gate_proj"][0].shape[0] % self.block[0]:
+        """As stored: ``(w13 e4m3 [n, 2I, H], its scales fp32 [n, 2I/128, H/128], w2 e4m3 [n, H, I], its scales)``."""
+        def as_bytes(t: torch.Tensor) -> torch.Tensor:  # cat / stack are not defined for float8 tensors
+            return t.view(torch.uint8)
+
+        columns: tuple[list, list, list, list] = ([], [], [], [])
+        for projections in self._projections(layer, experts):
+            for name, (weight, scales) in projections.items():
+                if weight.dtype != torch.float8_e4m3fn or scales is None:
+                    raise ValueError(f"layer {layer}: {name} is stored as {weight.dtype}, not block-scaled float8_e4m3fn")
+            (gate, gate_s), (up, up_s), (down, down_s) = (projections[name] for name in PROJECTIONS)
+            if gate.shape[0] % self.block[0]:
                 raise ValueError("gate/up rows must be a multiple of the scale block to be stacked")
-            q13.append(torch.cat([parts["gate_proj"][0].view(torch.uint8), parts["up_proj"][0].view(torch.uint8)]).view(torch.float8_e4m3fn))
-            s13.append(torch.cat([parts["gate_proj"][1], parts["up_proj"][1]]))
-            q2.append(parts["down_proj"][0])
-            s2.append(parts["down_proj"][1])
-        stack8 = lambda ts: torch.stack([t.view(torch.uint8) for t in ts]).view(torch.float8_e4m3fn)  # noqa: E731
-        return stack8(q13), torch.stack(s13), stack8(q2), torch.stack(s2)
+            columns[0].append(torch.cat((as_bytes(gate), as_bytes(up))))
+            columns[1].append(torch.cat((gate_s, up_s)).to(torch.float32))
+            columns[2].append(as_bytes(down))
+            columns[3].append(down_s.to(torch.float32))
+        w13, s13, w2, s2 = (torch.stack(column) for column in columns)
+        return w13.view(torch.float8_e4m3fn), s13, w2.view(torch.float8_e4m3fn), s2
 
     def router(self, layer: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Gate weight ``[E, H]`` and ``e_score_correction_bias [E]``, both fp32."""
-        base = PREFIX.format(layer=layer)
-        raw = self.get([f"{base}.gate.weight", f"{base}.gate.e_score_correction_bias"])
-        return raw[f"{base}.gate.weight"].to(torch.float32), raw[f"{base}.gate.e_score_correction_bias"].to(torch.float32)
+        """Gate weight ``[E, H]`` and selection bias ``e_score_correction_bias [E]``, both fp32."""
+        gate = PREFIX.format(layer=layer) + ".gate."
+        raw = self.get([gate + "weight", gate + "e_score_correction_bias"])
+        return raw[gate + "weight"].to(torch.float32), raw[gate + "e_score_correction_bias"].to(torch.float32)
