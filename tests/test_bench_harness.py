@@ -278,3 +278,32 @@ def test_timing_helpers_on_a_fake_device(monkeypatch):
     assert a == [1000.0] * 3 and b == [2000.0] * 3
     order = [t for t in fake.log if t in "AB"]
     assert order[-9:] == ["A", "B", "B"] * 3  # strictly alternating
+
+
+def test_headline_bench_clock_summary_and_cli_defaults():
+    """``bench.py`` is importable without a GPU; its clock sampler turns nvidia-smi lines into the median SM
+    clock, the maximum clock and the set of active throttle reasons."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("headline_bench", Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    sampler = bench.ClockSampler(0)
+    assert sampler.stop()["reasons"] == ["nvidia-smi unavailable"]  # never started
+
+    class Quiet:
+        def terminate(self): pass
+        def wait(self, timeout=None): return 0
+
+    sampler.proc = Quiet()
+    sampler.lines = [
+        "1965, 1965, 310.5, Not Active, Not Active, Not Active, Not Active",
+        "1350, 1965, 998.0, Not Active, Not Active, Not Active, Active",
+        "1410, 1965, 870.2, Not Active, Not Active, Not Active, Not Active",
+        "garbage line",
+        "[N/A], 1965, 1.0, Not Active, Not Active, Not Active, Not Active",
+    ]
+    summary = sampler.stop()
+    assert summary == {"sm_mhz": 1410.0, "sm_max_mhz": 1965.0, "power_w_max": 998.0, "samples": 3, "reasons": ["sw_power_cap"]}
