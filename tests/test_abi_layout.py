@@ -77,3 +77,22 @@ def test_plan_word_indices_match_the_header():
     for name in ("N_TILES", "SPLIT1", "SPLIT2", "N_ENTRIES", "SLOT_COLS", "VALID_ROWS", "WORDS"):
         value = int(re.search(rf"MF_PLAN_{name}\s*=\s*(\d+)", text).group(1))
         assert getattr(_lib, f"PLAN_{name}") == value
+
+
+def test_every_bound_function_is_declared_with_the_same_number_of_parameters():
+    """``ops/_lib.py`` sets ``argtypes`` per function; the header declares them.  Both lists must name the same
+    functions with the same arity, and the built library must export every one of them."""
+    text = re.sub(r"//[^\n]*", "", HEADER.read_text())
+    declared = {}
+    for match in re.finditer(r"\b(?:int|void|const char\*)\s+(mf_\w+)\s*\(([^;{]*)\)\s*;", text):
+        params = match.group(2).strip()
+        declared[match.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    if not _lib.LIB_PATH.exists() and shutil.which("nvcc") is None:
+        pytest.skip("native library not built and no nvcc")
+    handle = _lib.lib()
+    bound = {name: len(getattr(handle, name).argtypes) for name in declared if getattr(getattr(handle, name, None), "argtypes", None) is not None}
+    assert bound, "no bound functions found"
+    for name, arity in bound.items():
+        assert declared[name] == arity, f"{name}: header declares {declared[name]} parameters, ctypes binds {arity}"
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared but not exported by the library"
