@@ -10,13 +10,20 @@ routing, EP = N ranks, T tokens per rank (headline T = 128; the sweep covers 1..
 complete routed layer (router logits -> top-k -> dispatch -> experts -> return -> weighted merge)
 replayed from a CUDA graph.
 
+Correctness gate (both arms): before any timing of a capacity T, one replay is compared on every rank with
+the per-token loop oracle on the first min(T, 8) tokens; the verdicts are reduced with MIN over ranks and a
+point that fails is not timed (``oracle_err_max`` and ``status`` go into the JSON line).
+
 Timing protocol (both arms): W warm-up steps, then exactly K timed steps.  Before every step, outside
 the timed interval, the next input set of a rotating pool is copied into the static input buffers and
-a 256 MiB buffer is written to flush L2; ranks are aligned with a barrier; the step is bracketed by CUDA
-events on the launching stream; the per-rank sum over the K steps is reduced with MAX over ranks.
-SM clocks and throttle reasons are sampled with nvidia-smi while the steps run.
+a 256 MiB buffer is written to flush L2; ranks are aligned with a host barrier and then, on the device, by a
+one-element all-reduce enqueued on the launching stream right before the start event (so the ranks' streams
+enter the step together whatever the host-side jitter); the step is bracketed by CUDA events on the launching
+stream; the per-rank sum over the K steps is reduced with MAX over ranks, and the per-step times (MAX over
+ranks of each step) give min / median / max.  SM clocks and throttle reasons are sampled with nvidia-smi while
+the steps run.
 
-``e2e`` repeats the measurement through the public serving call (``GraphedMoELayer.__call__``): every
+``e2e`` repeats the measurement through the public serving call (``GraphedMoELayer.step``): every
 step copies that step's hidden states and logits from pinned host memory, replays, and copies the
 output rows back to pinned host memory, all inside the timed interval.
 
@@ -151,6 +158,25 @@ def make_local_weights(rank: int, world: int, dev: torch.device):
 
 
 ROUTING = "uniform"  # set from --dist
+DTYPE = "bf16"       # set from --dtype
+
+
+def make_local_weights_fp8(w13: torch.Tensor, w2: torch.Tensor):
+    """Block-scaled e4m3 pack of the local bf16 shard (one fp32 scale per 128x128 block) and a function that
+    returns the dequantised fp32 weights of a local expert for the oracle."""
+    from moeflow_b200.weights import dequant_block_fp8, quant_block_fp8
+
+    def pack(w):
+        qs, ss = zip(*(quant_block_fp8(w[e]) for e in range(w.shape[0])))
+        return torch.stack([q.view(torch.uint8) for q in qs]).view(torch.float8_e4m3fn), torch.stack(ss)
+
+    q13, s13 = pack(w13)
+    q2, s2 = pack(w2)
+
+    def expert_weights(e):
+        return dequant_block_fp8(q13[e], s13[e]).float().cpu(), dequant_block_fp8(q2[e], s2[e]).float().cpu()
+
+    return (q13, s13, q2, s2), expert_weights
 
 
 def make_inputs(tokens: int, rank: int, pool: int, pinned: bool):
@@ -186,7 +212,12 @@ class OurArm:
         from moeflow_b200.ops import _lib
 
         _lib.lib()  # the native library is mandatory here
-        self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, w13, w2, capacity=tokens, backend="cuda")
+        if DTYPE == "fp8":
+            q13, s13, q2, s2 = w13  # block-scaled e4m3 pack (see make_local_weights_fp8); w2 is unused
+            self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, None, None, capacity=tokens, backend="cuda", device=dev)
+            self.layer.set_weights_fp8(q13, s13, q2, s2)
+        else:
+            self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, w13, w2, capacity=tokens, backend="cuda")
         self.g = GraphedMoELayer(self.layer, bias).capture()
         self.x, self.logits = self.g.x, self.g.logits
         self.launches = self.g.kernels_per_step
@@ -194,8 +225,23 @@ class OurArm:
     def replay(self):
         return self.g.replay()
 
-    def call(self, x, lg, out):
-        return self.g(x, lg, out)
+    def stage_inputs(self, xs_h, lgs_h):
+        """The public call takes one pinned block per step: hidden rows, logits and the row count packed as the
+        layer lays them out, so that a step needs a single host-to-device copy."""
+        staged = []
+        for x, lg in zip(xs_h, lgs_h):
+            blk = self.g.new_pinned_inputs()
+            blk.x[: x.shape[0]].copy_(x)
+            blk.logits[: lg.shape[0]].copy_(lg)
+            blk.set_rows(x.shape[0])
+            staged.append(blk)
+        return staged
+
+    def call(self, staged, out):
+        return self.g.step(staged, out)
+
+    def h2d_bytes(self, tokens):
+        return self.g.packed_bytes
 
     def check(self):
         st = self.layer.check_status()
@@ -239,12 +285,19 @@ class ReferenceArm:
         self.graph.replay()
         return self.out
 
-    def call(self, x, lg, out):
+    def stage_inputs(self, xs_h, lgs_h):
+        return list(zip(xs_h, lgs_h))
+
+    def call(self, staged, out):
+        x, lg = staged
         self.x.copy_(x, non_blocking=True)
         self.logits.copy_(lg, non_blocking=True)
         self.graph.replay()
         out.copy_(self.out, non_blocking=True)
         return out
+
+    def h2d_bytes(self, tokens):
+        return tokens * HIDDEN * 2 + tokens * EXPERTS * 4
 
     def check(self):
         pass
@@ -254,10 +307,59 @@ class ReferenceArm:
 
 
 # ------------------------------------------------------------------------------------------------
+# correctness gate
+# ------------------------------------------------------------------------------------------------
+def oracle_gate(out, x, logits, bias, expert_weights, rank, world, dev, n_check=8) -> dict:
+    """First ``min(T, n_check)`` tokens of this rank against the per-token loop oracle; MIN over ranks.
+
+    ``expert_weights(e) -> (w13 [2I, H], w2 [H, I])`` returns fp32 CPU copies of a *local* expert (for the fp8
+    arm: the dequantised weights).  Ranks exchange only the experts the checked tokens need.
+    """
+    from moeflow_b200 import GLM53_FLASH_I1536 as cfg
+    from moeflow_b200.reference import moe_reference, route_reference
+    from moeflow_b200.tolerances import normwise_rel_err
+
+    n = min(n_check, x.shape[0])
+    per = EXPERTS // world
+    routes = route_reference(logits[:n].float().cpu(), bias.float().cpu(), cfg)
+    need = sorted({e for r in routes for e, _ in r})
+    if world > 1:
+        wanted = [None] * world
+        dist.all_gather_object(wanted, need)
+        serve = sorted({e for lst in wanted for e in lst if e // per == rank})
+        have = {e: expert_weights(e - rank * per) for e in serve}
+        parts = [None] * world
+        dist.all_gather_object(parts, have)
+        table = {e: t for part in parts for e, t in part.items()}
+    else:
+        table = {e: expert_weights(e) for e in need}
+
+    class _Lookup:
+        def __init__(self, which):
+            self.which = which
+
+        def __getitem__(self, e):
+            return table[e][self.which]
+
+    ref = moe_reference(x[:n].cpu(), logits[:n].float().cpu(), None, _Lookup(0), _Lookup(1), cfg, routes=routes)
+    got = out[:n].float().cpu()
+    err = normwise_rel_err(got, ref.float()) if n else 0.0
+    finite = bool(torch.isfinite(got).all())
+    tol = 0.06 if DTYPE == "fp8" else 4 * 2.0**-8  # e4m3 activations: a few percent is the format
+    ok = finite and err <= tol
+    verdict = torch.tensor([1.0 if ok else 0.0, -err], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    return {"passed": bool(verdict[0].item() == 1.0), "err_max": float(-verdict[1].item()), "tolerance": tol,
+            "tokens_checked": n}
+
+
+# ------------------------------------------------------------------------------------------------
 # timing
 # ------------------------------------------------------------------------------------------------
-def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush: torch.Tensor) -> float:
-    """Sum of the device times of ``steps`` steps in ms (this rank).  prepare_fn(i) runs untimed."""
+def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush: torch.Tensor, dev) -> list[float]:
+    """Device times of ``steps`` steps in ms (this rank).  prepare_fn(i) runs untimed."""
+    align = torch.zeros(1, dtype=torch.float32, device=dev)
     for i in range(warmup):
         prepare_fn(i)
         flush.zero_()
@@ -272,7 +374,8 @@ def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush:
         prepare_fn(warmup + i)
         flush.zero_()
         if world > 1:
-            dist.barrier()
+            dist.barrier()            # host alignment: no rank runs a step ahead
+            dist.all_reduce(align)    # device alignment: enqueued, not waited for; the streams leave it together
         starts[i].record()
         step_fn(warmup + i)
         ends[i].record()
@@ -280,18 +383,20 @@ def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush:
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    return sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    return [s.elapsed_time(e) for s, e in zip(starts, ends)]
 
 
-def max_over_ranks(v: float, world: int, dev) -> float:
-    if world == 1:
-        return v
-    t = torch.tensor([v], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+def reduce_times(ms: list[float], world: int, dev) -> dict:
+    """``value``: MAX over ranks of the per-rank sum / steps.  Spread: per-step MAX over ranks."""
+    t = torch.tensor(ms + [sum(ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    per_step = sorted(float(v) * 1e3 for v in t[:-1].tolist())
+    return {"us": float(t[-1].item()) * 1e3 / len(ms), "min": per_step[0], "median": per_step[len(per_step) // 2],
+            "max": per_step[-1]}
 
 
-def measure(arm_cls, rank, world, dev, w13, w2, bias, tokens, steps, warmup, flush):
+def measure(arm_cls, rank, world, dev, w13, w2, bias, tokens, steps, warmup, flush, expert_weights):
     arm = arm_cls(rank, world, dev, w13, w2, bias, tokens)
     xs_h, lgs_h = make_inputs(tokens, rank, POOL, pinned=True)
     xs_d = [x.to(dev) for x in xs_h]
@@ -302,18 +407,30 @@ def measure(arm_cls, rank, world, dev, w13, w2, bias, tokens, steps, warmup, flu
         arm.x.copy_(xs_d[i % POOL])
         arm.logits.copy_(lgs_d[i % POOL])
 
-    dev_ms = timed_steps(lambda i: arm.replay(), prepare, steps, warmup, world, flush)
+    # gate: one replay on input set 0, all ranks against the oracle, before any sample is taken
+    prepare(0)
+    out = arm.replay()
+    torch.cuda.synchronize()
+    gate = oracle_gate(out, xs_h[0], lgs_h[0], bias, expert_weights, rank, world, dev)
     arm.check()
-    e2e_ms = timed_steps(lambda i: arm.call(xs_h[i % POOL], lgs_h[i % POOL], out_h), lambda i: None, steps, warmup,
-                         world, flush)
+    if not gate["passed"]:
+        arm.close()
+        raise RuntimeError(f"oracle gate failed at T={tokens}: {gate}")
+
+    dev_ms = timed_steps(lambda i: arm.replay(), prepare, steps, warmup, world, flush, dev)
+    arm.check()
+    staged = arm.stage_inputs(xs_h, lgs_h)  # the arm's pinned input sets for its public call
+    e2e_ms = timed_steps(lambda i: arm.call(staged[i % POOL], out_h), lambda i: None, steps, warmup, world, flush, dev)
     arm.check()
     finite = bool(torch.isfinite(out_h.float()).all())
+    d, e = reduce_times(dev_ms, world, dev), reduce_times(e2e_ms, world, dev)
     res = {
-        "us_per_step": max_over_ranks(dev_ms, world, dev) * 1e3 / steps,
-        "e2e_us_per_step": max_over_ranks(e2e_ms, world, dev) * 1e3 / steps,
+        "us_per_step": d["us"], "spread_us": {k: round(d[k], 2) for k in ("min", "median", "max")},
+        "e2e_us_per_step": e["us"], "e2e_spread_us": {k: round(e[k], 2) for k in ("min", "median", "max")},
         "launches_per_step": arm.launches,
         "finite": finite,
-        "h2d_bytes": tokens * HIDDEN * 2 + tokens * EXPERTS * 4,
+        "oracle": gate,
+        "h2d_bytes": arm.h2d_bytes(tokens),
         "d2h_bytes": tokens * HIDDEN * 2,
     }
     arm.close()
@@ -331,14 +448,20 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=128, help="headline tokens per rank")
     ap.add_argument("--no-sweep", action="store_true", help="skip the T = 1..128 sweep")
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"], help="routing popularity profile")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="fp8: block-scaled e4m3 expert weights (128x128 blocks) and 1x128 e4m3 activations, bf16 in/out")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    global ROUTING
+    global ROUTING, DTYPE
     ROUTING = args.dist
+    DTYPE = args.dtype
 
     if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "moeflow" / "fixed.py").exists():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip --target install of the reference checkout)"}))
+        return
+    if args.impl == "reference" and args.dtype == "fp8":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's fixed-capacity layer has no fp8 expert path of its own (it dequantises to bf16 or calls the serving engine's experts)"}))
         return
     rank, world, dev = init_dist(args.gpus)
     if args.impl == "reference":
@@ -352,6 +475,15 @@ def main() -> None:
     arm_cls = ReferenceArm if args.impl == "reference" else OurArm
 
     w13, w2 = make_local_weights(rank, world, dev)
+    if args.dtype == "fp8":
+        pack, expert_weights = make_local_weights_fp8(w13, w2)
+        w13, w2 = pack, None
+    else:
+        w13_ref, w2_ref = w13, w2
+
+        def expert_weights(e):
+            return w13_ref[e].float().cpu(), w2_ref[e].float().cpu()
+
     bias = (0.05 * torch.randn(EXPERTS, generator=torch.Generator().manual_seed(99))).to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
@@ -359,7 +491,7 @@ def main() -> None:
     if rank == 0:
         sampler.start()
     try:
-        head = measure(arm_cls, rank, world, dev, w13, w2, bias, args.tokens, args.steps, args.warmup, flush)
+        head = measure(arm_cls, rank, world, dev, w13, w2, bias, args.tokens, args.steps, args.warmup, flush, expert_weights)
     except Exception as exc:
         if args.impl == "reference":
             if rank == 0:
@@ -367,19 +499,21 @@ def main() -> None:
             return
         raise
     clocks = sampler.stop() if rank == 0 else {}
-    per_t = {}
+    per_t, per_t_err = {}, {}
     if not args.no_sweep:
         for t in SWEEP:
             if t == args.tokens:
                 per_t[str(t)] = round(head["us_per_step"], 2)
+                per_t_err[str(t)] = round(head["oracle"]["err_max"], 5)
                 continue
             try:
-                r = measure(arm_cls, rank, world, dev, w13, w2, bias, t, args.steps, args.warmup, flush)
+                r = measure(arm_cls, rank, world, dev, w13, w2, bias, t, args.steps, args.warmup, flush, expert_weights)
                 per_t[str(t)] = round(r["us_per_step"], 2)
+                per_t_err[str(t)] = round(r["oracle"]["err_max"], 5)
             except Exception as exc:  # a sweep point never hides the headline
-                per_t[str(t)] = f"failed: {type(exc).__name__}"
+                per_t[str(t)] = f"failed: {type(exc).__name__}: {exc}"[:120]
     if rank == 0:
-        pub = PUBLISHED_US.get((world, args.tokens))
+        pub = PUBLISHED_US.get((world, args.tokens)) if args.dtype == "bf16" else None
         launches = head["launches_per_step"]
         line = {
             "metric": "routed_moe_layer_us_per_step_graph_replay_max_over_ranks",
@@ -393,7 +527,7 @@ def main() -> None:
             "higher_is_better": False,
             "scaling": "weak",
             "vs_baseline": round(head["us_per_step"] / pub, 4) if pub else None,
-            "dtype": "bf16",
+            "dtype": "bf16" if args.dtype == "bf16" else "fp8_e4m3 experts (128x128 weight blocks, 1x128 activation groups), bf16 in/out",
             "data": "synthetic tokens and uniform router logits, random-init weights N(0, 0.02-scale) of the named shape",
             "config": {
                 "model": "GLM-5.3-Flash routed MoE layer (hidden 4096, 288 experts, top-8, intermediate 1536)",
@@ -403,15 +537,21 @@ def main() -> None:
                 "parallelism": f"ep{world}",
                 "routing": args.dist,
                 "l2": "256 MiB buffer written before every timed step (L2 flush); local expert weights >> L2",
-                "timing": "per-step CUDA events, barrier-aligned, sum over steps, max over ranks",
+                "timing": "per-step CUDA events; host barrier, then a one-element all-reduce on the stream before the start event (device-side alignment of the ranks); sum over steps, max over ranks",
                 "published_baseline_note": "published number is EP=4, intermediate 2048, real weights, L2-warm replays",
             },
             "per_T_us": per_t,
+            "per_T_oracle_err": per_t_err,
+            "spread_us": head["spread_us"],
+            "oracle_err_max": round(head["oracle"]["err_max"], 6),
+            "oracle_tolerance": head["oracle"]["tolerance"],
+            "status": "ok" if head["oracle"]["passed"] else "oracle gate failed",
             "e2e": {
                 "value": round(head["e2e_us_per_step"], 3),
                 "unit": "us/step",
                 "h2d_bytes_per_step": head["h2d_bytes"],
                 "d2h_bytes_per_step": head["d2h_bytes"],
+                "spread_us": head["e2e_spread_us"],
             },
             "gpu_launches": (launches * args.steps) if launches else None,
             "finite": head["finite"],

@@ -85,6 +85,13 @@ __device__ __forceinline__ void publish_flags(const unsigned long long* peer_fla
   __threadfence_system();
   for (int d = 0; d < n_peers; ++d) st_relaxed_sys_u32(reinterpret_cast<unsigned*>(peer_flag[d]) + rank, value);
 }
+// Counting flags: every CTA that has finished its share of a transfer adds one to word [rank] of the
+// destination's flag array, after a system-scope fence that orders the CTA's peer stores before it.  The
+// waiter knows how many arrivals a forward brings (epoch * arrivals per forward), so no CTA has to be the
+// last one and no second fence or local counter sits between the data and the flag.
+__device__ __forceinline__ void red_add_relaxed_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ unsigned ld_relaxed_sys_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -8,8 +8,11 @@
 // t < *num_valid).  Rows t >= T get valid = 0 and all-empty slots; their hidden lanes stay stale.
 //
 // The kernel writes every row straight into the owner's receive buffer with plain 16-byte stores
-// through the peer mapping (NVLink), then the last CTA to finish publishes this forward's epoch
-// in every owner's flag word [s] with a system-scope release store.  No NCCL call, no staging buffer.
+// through the peer mapping (NVLink).  Every CTA (one per token position) then fences once at system
+// scope and adds one to flag word [s] of every owner: the flags count arrivals, a forward brings exactly
+// C of them per source, and the owner's metadata kernel waits for epoch * C.  No CTA has to be the last
+// one, so no second fence and no local counter sit between the rows and the flag.  No NCCL call, no
+// staging buffer.
 //
 // Replaces the reference's pack kernel plus its dispatch all_to_all_single
 // (moeflow/kernels/dispatch_pack.py:10-95, moeflow/fixed.py:95-125,234).
@@ -105,16 +108,19 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
     }
   }
 
-  // Publish: the barrier orders every thread's stores before thread 0's system fence (cumulative), then
-  // the CTA counts itself done.
+  // Publish: the barrier orders every thread's stores before the system fence of warp 0's lanes (cumulative);
+  // then one arrival per destination, issued by different lanes so that they travel together.
   __syncthreads();
-  if (tid == 0) {
+  if (tid < 32) {
     __threadfence_system();
-    const unsigned done = atomicAdd(a.done_counter, 1u);
-    if (done == gridDim.x - 1) {
-      *a.done_counter = 0u;
-      *a.epoch = epoch_next;
-      publish_flags(a.peer_flag, a.R, a.rank, epoch_next);
+    for (int d = tid; d < a.R; d += 32) red_add_relaxed_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, 1u);
+    if (tid == 0) {
+      // the local epoch (read by this rank's later kernels after this grid has completed)
+      const unsigned done = atomicAdd(a.done_counter, 1u);
+      if (done == gridDim.x - 1) {
+        *a.done_counter = 0u;
+        *a.epoch = epoch_next;
+      }
     }
   }
 }

@@ -78,6 +78,15 @@ __host__ __device__ __forceinline__ int choose_split(int units, int k_blocks, in
   return best;
 }
 
+// The K cut of one GEMM: stream-K (0) when asked for, the units do not fill many rounds of the persistent CTAs
+// (below 8 units per CTA an uneven last round costs more than the partial tiles of the cut units) and the
+// scratch holds the two partial tiles a CTA may need; else the K split of choose_split.
+__device__ __forceinline__ int choose_cut(const mf_meta_args& a, int units, int k_blocks, int slots, int overhead_kb,
+                                          int cols) {
+  if (a.stream_k && units > 0 && units < 8 * a.n_sms && units % a.n_sms != 0 && slots >= 2 * a.n_sms) return 0;
+  return choose_split(units, k_blocks, a.n_sms, slots, overhead_kb, cols);
+}
+
 __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta_args a) {
   extern __shared__ int sm[];
   const int L = a.L, K = a.K;
@@ -92,8 +101,10 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
 
+  // counting flags: every source adds one per token position (rows / R of them) in every forward
   if (a.flags != nullptr && tid < a.R) {
-    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kDispatchFlagTimeout, tid, 0, epoch);
+    if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)(a.rows / a.R), a.wait_ns))
+      report_status(a.status, kDispatchFlagTimeout, tid, 0, epoch);
   }
   for (int i = tid; i < a.n_counters1; i += kMetaThreads) a.counters1[i] = 0;
   for (int i = tid; i < a.n_counters2; i += kMetaThreads) a.counters2[i] = 0;
@@ -209,8 +220,8 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
       cols = 0;  // fixed slots of the kernel's n_max columns
     }
     a.plan[MF_PLAN_N_TILES] = nt;
-    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4, wide_cols);
-    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8, wide_cols);
+    a.plan[MF_PLAN_SPLIT1] = choose_cut(a, nt * a.m_blocks1, a.k_blocks1, slots1, 4, wide_cols);
+    a.plan[MF_PLAN_SPLIT2] = choose_cut(a, nt * a.m_blocks2, a.k_blocks2, slots2, 8, wide_cols);
     a.plan[MF_PLAN_N_ENTRIES] = n_entries;
     a.plan[MF_PLAN_SLOT_COLS] = cols;
     a.plan[MF_PLAN_VALID_ROWS] = warp_sums[35];
@@ -319,7 +330,8 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_count_kernel(const m
   grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
   if (a.flags != nullptr && tid < a.R) {
-    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kDispatchFlagTimeout, tid, cta, epoch);
+    if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)(a.rows / a.R), a.wait_ns))
+      report_status(a.status, kDispatchFlagTimeout, tid, cta, epoch);
   }
   for (int i = cta * kMetaThreads + tid; i < a.n_counters1; i += n_ctas * kMetaThreads) a.counters1[i] = 0;
   for (int i = cta * kMetaThreads + tid; i < a.n_counters2; i += n_ctas * kMetaThreads) a.counters2[i] = 0;
@@ -424,8 +436,8 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const m
       cols = 0;
     }
     a.plan[MF_PLAN_N_TILES] = nt;
-    a.plan[MF_PLAN_SPLIT1] = choose_split(nt * a.m_blocks1, a.k_blocks1, a.n_sms, slots1, 4, wide_cols);
-    a.plan[MF_PLAN_SPLIT2] = choose_split(nt * a.m_blocks2, a.k_blocks2, a.n_sms, slots2, 8, wide_cols);
+    a.plan[MF_PLAN_SPLIT1] = choose_cut(a, nt * a.m_blocks1, a.k_blocks1, slots1, 4, wide_cols);
+    a.plan[MF_PLAN_SPLIT2] = choose_cut(a, nt * a.m_blocks2, a.k_blocks2, slots2, 8, wide_cols);
     a.plan[MF_PLAN_N_ENTRIES] = n_entries;
     a.plan[MF_PLAN_SLOT_COLS] = cols;
     a.plan[MF_PLAN_VALID_ROWS] = a.acc[0];
@@ -467,7 +479,10 @@ extern "C" int mf_plan_split(int units, int k_blocks, int n_sms, int max_slots, 
 extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
   if (!a || a->L < 1 || a->L > mf::kMetaThreads || a->R > mf::kMetaThreads || a->block_m < 1) return -1;
   const size_t smem = ((size_t)mf::kMetaWarps * a->L + 2 * (size_t)a->L + 40) * sizeof(int);
-  static size_t configured = 0;
+  static size_t configured_all[64] = {};  // per device: the attribute belongs to (function, device)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  size_t& configured = configured_all[dev];
   if (smem > 48 * 1024 && smem > configured) {
     cudaError_t e =
         cudaFuncSetAttribute(mf::expert_meta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

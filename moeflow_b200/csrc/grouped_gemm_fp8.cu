@@ -401,19 +401,21 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
 // bounded by a device-side row count (n_rows_dev, e.g. the plan's entry count).
 // -------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-quant_rows_kernel(const uint8_t* __restrict__ x, long long x_pitch, const int* __restrict__ row_index, int hidden,
-                  uint8_t* __restrict__ q, float* __restrict__ scales, long long valid_off, const int* n_rows_dev) {
+quant_rows_kernel(const uint8_t* x, long long x_pitch, const int* row_index, int hidden, uint8_t* q, float* scales,
+                  long long valid_off, const int* n_rows_dev) {
+  // Inputs are produced by kernels that may still run while this one is resident (programmatic launch), so
+  // they are read from L2 (ld.global.cg), never through the non-coherent read-only path.
   grid_dep_launch();
   grid_dep_wait();
   const int r = blockIdx.x;
-  if (n_rows_dev != nullptr && r >= *n_rows_dev) return;
-  const long long src = row_index ? (long long)row_index[r] : (long long)r;
+  if (n_rows_dev != nullptr && r >= __ldcg(n_rows_dev)) return;
+  const long long src = row_index ? (long long)__ldcg(row_index + r) : (long long)r;
   const uint8_t* row = x + src * x_pitch;
-  if (valid_off >= 0 && *reinterpret_cast<const int*>(row + valid_off) == 0) return;
+  if (valid_off >= 0 && __ldcg(reinterpret_cast<const int*>(row + valid_off)) == 0) return;
   const int chunks = hidden / 8;
   const int groups = hidden / 128;
   for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-    const uint4 v = reinterpret_cast<const uint4*>(row)[c];
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(row) + c);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
     float f[8];
     float amax = 0.f;
@@ -448,12 +450,15 @@ typedef CUresult (*F8EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
 template <bool kGateUp, int N_MAX>
 static int launch_f8(const void* tmap, const mf_gemm_args* args, int grid, cudaStream_t stream) {
   using Cfg = F8Cfg<kGateUp, N_MAX>;
-  static bool configured = false;
+  static bool configured[64] = {};  // per device: the attribute belongs to (function, device)
   auto kern = grouped_gemm_fp8_kernel<kGateUp, N_MAX>;
-  if (!configured) {
+  int dev = 0;
+  cudaError_t de = cudaGetDevice(&dev);
+  if (de != cudaSuccess) return (int)de;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   CUtensorMap tm;
   memcpy(&tm, tmap, sizeof(tm));

@@ -10,10 +10,16 @@
 //   down     : acc[128, n] = W2[e, mb*128 + r, :] . ACT[n, :]
 //              out[entry, mb*128 + r] = bf16( row_scale[entry] * acc )
 //
-// Work units are (token tile, 128-row weight block, K split).  The token tiles and the K split come
-// from a device-side plan (see expert_meta.cu), so nothing is read back to the host.  With a K split
-// S > 1 every unit stores its fp32 partial sums and the last unit to arrive (per 32-row quarter)
-// adds the S partials in split order 0..S-1, so the result does not depend on arrival order.
+// A unit is (token tile, 128-row weight block); it needs k_blocks K steps.  The token tiles and the way
+// the units are cut along K come from a device-side plan (see expert_meta.cu), so nothing is read back
+// to the host.  Two cuts exist:
+//   * K split S in {1, 2, 4, 8} (plan word = S): every unit is cut into S equal segments, segments are
+//     dealt to the CTAs round-robin;
+//   * stream-K (plan word = 0): the units' K steps are laid end to end and every CTA takes one contiguous
+//     share of that line, so all CTAs stream the same number of weight bytes whatever the unit count
+//     (no partly filled last round); a unit that straddles CTA boundaries is cut there.
+// A segment that is not a whole unit stores its fp32 partial sums; the last segment to arrive (per
+// 32-row quarter) adds the segments in K order, so the result does not depend on arrival order.
 //
 // Warp roles (256 threads, one CTA per SM, persistent over units blockIdx.x, +gridDim.x, ...):
 //   warp 0      TMA producer for the weight tiles (lane 0 issues)
@@ -39,6 +45,7 @@ constexpr int kThreadsWithReturn = 384;  // + 4 return warps (fused owner reduce
 constexpr int kRetDepth = 4;            // queued unit descriptors per quarter
 constexpr int kGatherThreads = 64;
 constexpr int kAccStages = 2;
+constexpr int kMaxDevices = 64;        // devices one process may drive (per-device launch configuration)
 
 template <bool kGateUp, int N_MAX>
 struct GemmCfg {
@@ -62,6 +69,99 @@ struct PipeState {
       stage = 0;
       phase ^= 1u;
     }
+  }
+};
+
+// One piece of work of a CTA: `nkb` K steps of unit (tt, mb) starting at K block kb0.
+struct Seg {
+  int unit, tt, mb;
+  int e, row_start, n_rows;  // the token tile: expert, first entry, entries
+  int kb0, nkb;
+  int nseg, seg;             // segments of this unit and this one's index in K order (nseg == 1: whole unit)
+  int c_first;               // stream-K: CTA that holds segment 0 of the unit
+};
+
+// Enumerates the segments of CTA `cta`.  Every warp role builds its own iterator from the same plan words
+// and therefore walks the same sequence.
+struct WorkIter {
+  const mf_gemm_args* a;
+  int n_max, m_blocks, KB, split, stream;
+  int units;         // n_tiles * m_blocks
+  int cta, G;        // this CTA, CTAs that take part
+  long long W;       // stream-K: units * KB
+  long long w, w1;   // stream-K: cursor and end of this CTA's share
+  int u;             // K split: next (unit, split) index
+  bool bad_tile;     // a tile wider than the kernel's token tile was met (and skipped)
+
+  __device__ __forceinline__ long long share_begin(int c) const { return (long long)c * W / G; }
+  // CTA holding K step x of the line (the largest c with share_begin(c) <= x)
+  __device__ __forceinline__ int cta_of(long long x) const { return (int)(((x + 1) * G + W - 1) / W) - 1; }
+
+  __device__ __forceinline__ void init(const mf_gemm_args& args, int n_max_, int n_tiles, int split_, int cta_, int grid) {
+    a = &args;
+    n_max = n_max_;
+    m_blocks = args.m_blocks;
+    KB = args.k_blocks;
+    split = split_ < 1 ? 1 : split_;
+    stream = split_ == 0;
+    units = n_tiles * m_blocks;
+    cta = cta_;
+    W = (long long)units * KB;
+    G = stream ? (int)(W < (long long)grid ? W : (long long)grid) : grid;
+    bad_tile = false;
+    u = cta;
+    w = w1 = 0;
+    if (stream && cta < G) {
+      w = share_begin(cta);
+      w1 = share_begin(cta + 1);
+    }
+  }
+
+  __device__ __forceinline__ bool next(Seg& s) {
+    while (true) {
+      if (stream) {
+        if (w >= w1) return false;
+        s.unit = (int)(w / KB);
+        s.kb0 = (int)(w - (long long)s.unit * KB);
+        const long long left = w1 - w;
+        s.nkb = (KB - s.kb0) < left ? (KB - s.kb0) : (int)left;
+        w += s.nkb;
+        const long long x0 = (long long)s.unit * KB;
+        s.c_first = cta_of(x0);
+        s.nseg = cta_of(x0 + KB - 1) - s.c_first + 1;
+        s.seg = cta - s.c_first;
+      } else {
+        if (u >= units * split) return false;
+        const int ks = u % split;
+        s.unit = u / split;
+        u += G;
+        s.nkb = KB / split;
+        s.kb0 = ks * s.nkb;
+        s.nseg = split;
+        s.seg = ks;
+        s.c_first = 0;
+      }
+      s.tt = s.unit / m_blocks;
+      s.mb = s.unit - s.tt * m_blocks;
+      s.e = a->tile_e[s.tt];
+      s.row_start = a->tile_s[s.tt];
+      s.n_rows = a->tile_n[s.tt];
+      if ((unsigned)s.n_rows <= (unsigned)n_max) return true;
+      bad_tile = true;  // a plan built for wider tiles than this kernel: skip the segment, every role alike
+    }
+  }
+
+  // Partial-sum slot of segment `sg` of the unit of `s`.  K split: slots are (unit, segment).  Stream-K: every
+  // CTA owns two slots, one for the segment its share starts with and one for the segment it ends with.
+  __device__ __forceinline__ int slot_of(const Seg& s, int sg) const {
+    if (!stream) return s.unit * split + sg;
+    const int c = s.c_first + sg;
+    return 2 * c + (share_begin(c) >= (long long)s.unit * KB ? 0 : 1);
+  }
+  // Slots the plan needs (for the capacity check).
+  __device__ __forceinline__ long long slots_needed() const {
+    if (stream) return 2ll * G;
+    return split > 1 ? (long long)units * split : 0;
   }
 };
 
@@ -141,7 +241,7 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
     const unsigned before = atomicAdd(a.ret_done, (unsigned)completed);
     if (before + (unsigned)completed == total) {
       *a.ret_done = 0u;
-      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch);
+      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch * (unsigned)a.ret_C);  // counting flags: C arrivals per forward
     }
   }
 }
@@ -226,28 +326,44 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     // Fused return path with nothing to return: the flags must still be published (thread 64 belongs to
     // the warps that waited for the previous kernel).
     if (a.plan[MF_PLAN_VALID_ROWS] == 0) {
-      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch);
+      publish_flags(a.ret_flag, a.ret_R, a.ret_rank, *a.ret_epoch * (unsigned)a.ret_C);
     }
   }
-  const int n_tiles = a.plan[MF_PLAN_N_TILES];
-  int split = a.plan[a.split_word];
-  if (split < 1) split = 1;
-  const int kb_per = a.k_blocks / split;
-  const int total_units = n_tiles * a.m_blocks * split;
+  // ---- the plan: tile count and the K cut, checked against what the caller's buffers can hold -----------
+  int n_tiles = a.plan[MF_PLAN_N_TILES];
+  const int cut = a.plan[a.split_word];  // 0 = stream-K, else the K split
+  int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
+  if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
+  const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kBlockM;
   const unsigned long long wait_ns = a.wait_ns;
+  WorkIter work;
+  work.init(a, N_MAX, n_tiles, cut, blockIdx.x, gridDim.x);
+  {
+    // A plan that does not fit the buffers it indexes (a tile count or a cut larger than what the caller
+    // sized the scratch for) is refused here, on the device, before anything is stored: every thread of
+    // every CTA sees the same words and takes the same branch.
+    bool bad = n_tiles < 0 || !(cut == 0 || cut == 1 || cut == 2 || cut == 4 || cut == 8) ||
+               (cut > 1 && a.k_blocks % cut != 0);
+    bad = bad || (a.max_tiles > 0 && n_tiles > a.max_tiles);
+    bad = bad || (a.n_counters > 0 && (long long)n_tiles * a.m_blocks * 4 > (long long)a.n_counters);
+    bad = bad || (a.partial_floats > 0 && work.slots_needed() * slot_floats > a.partial_floats);
+    if (bad) {
+      if (tid == 0) report_status(a.status, kBadArgument, 6, blockIdx.x, 0);
+      n_tiles = 0;
+      work.init(a, N_MAX, 0, 1, blockIdx.x, gridDim.x);
+    }
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ weight TMA producer
     PipeState st;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int ks = u % split;
-      const int mb = (u / split) % a.m_blocks;
-      const int tt = u / (split * a.m_blocks);
-      const int e = a.tile_e[tt];
-      const int row0 = e * a.rows_per_expert + mb * kBlockM;
-      for (int j = 0; j < kb_per; ++j) {
-        const int kb = ks * kb_per + j;
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const int row0 = sg.e * a.rows_per_expert + sg.mb * kBlockM;
+      for (int j = 0; j < sg.nkb; ++j) {
+        const int kb = sg.kb0 + j;
         ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -274,10 +390,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     // ------------------------------------------------------------------ UMMA issuer
     PipeState st, acc;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt];
-      const uint32_t n_tile = (uint32_t)((n_rows + 15) & ~15);
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const uint32_t n_tile = (uint32_t)((sg.n_rows + 15) & ~15);
       const uint32_t idesc = umma_idesc(1, 1, kBlockM, n_tile < 16 ? 16 : n_tile);
       ok = mbar_wait_bounded(&acc_empty[acc.stage], acc.phase ^ 1u, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
@@ -287,7 +403,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       tc_fence_after_sync();
       const uint32_t d0 = tmem_base + acc.stage * Cfg::kAccCols;
-      for (int j = 0; j < kb_per; ++j) {
+      for (int j = 0; j < sg.nkb; ++j) {
         ok = mbar_wait_bounded(&full_bar[st.stage], st.phase, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (trace && lane == 0 && trace[3] == 0) trace[3] = global_timer_ns();
@@ -322,12 +438,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (warp == 2) {
       PipeState st;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        const int ks = u % split;
-        const int tt = u / (split * a.m_blocks);
-        const int row_start = a.tile_s[tt];
-        for (int j = 0; j < kb_per; ++j) {
-          const int kb = ks * kb_per + j;
+      WorkIter it = work;
+      Seg sg;
+      while (ok && it.next(sg)) {
+        for (int j = 0; j < sg.nkb; ++j) {
+          const int kb = sg.kb0 + j;
           ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
@@ -339,7 +454,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             // entries, or zero fill past the end of the buffer) land in smem rows the MMA does not read
             // or in accumulator columns the epilogue skips
             mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageB);
-            tma_load_2d(sB + st.stage * Cfg::kStageB, &tmap_b, &full_bar[st.stage], kb * 64, row_start);
+            tma_load_2d(sB + st.stage * Cfg::kStageB, &tmap_b, &full_bar[st.stage], kb * 64, sg.row_start);
           }
           __syncwarp();
           st.advance(STAGES);
@@ -358,11 +473,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     const uint32_t sw_off = (uint32_t)((chunk ^ r_in) << 4);
     PipeState st;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int ks = u % split;
-      const int tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt];
-      const int row_start = a.tile_s[tt];
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const int n_rows = sg.n_rows;
       int n_tile = (n_rows + 15) & ~15;
       if (n_tile < 16) n_tile = 16;
       const uint8_t* rp[N_MAX / 8];
@@ -371,12 +485,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int n = r_in + 8 * i;
         rp[i] = nullptr;
         if (n < n_rows) {
-          const long long idx = a.b_index ? (long long)a.b_index[row_start + n] : (long long)(row_start + n);
+          const long long idx = a.b_index ? (long long)a.b_index[sg.row_start + n] : (long long)(sg.row_start + n);
           rp[i] = static_cast<const uint8_t*>(a.b_base) + idx * a.b_pitch + chunk * 16;
         }
       }
-      for (int j = 0; j < kb_per; ++j) {
-        const int kb = ks * kb_per + j;
+      for (int j = 0; j < sg.nkb; ++j) {
+        const int kb = sg.kb0 + j;
         ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -425,12 +539,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       rq.advance(kRetDepth);
       return true;
     };
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int ks = u % split;
-      const int mb = (u / split) % a.m_blocks;
-      const int tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt];
-      const int row_start = a.tile_s[tt];
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const int mb = sg.mb;
+      const int n_rows = sg.n_rows;
+      const int row_start = sg.row_start;
       int n_tile = (n_rows + 15) & ~15;
       if (n_tile < 16) n_tile = 16;
       ok = mbar_wait_bounded(&acc_full[acc.stage], acc.phase, abort_flag, wait_ns);
@@ -445,7 +559,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
       const long long out_col = (long long)mb * kBlockM + row;
 
-      if (split == 1) {
+      if (sg.nseg == 1) {
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           uint32_t g[16], up[16];
           tmem_ld_16(taddr + c0, g);
@@ -475,12 +589,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
         if (with_return) ok = enqueue_return(n_rows, row_start, mb);
       } else {
-        // Split K: park the fp32 partial sums, then the last quarter-warp to arrive reduces them.
-        const int tile_mb = tt * a.m_blocks + mb;
-        int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
-        if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
-        const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kBlockM;
-        float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
+        // The unit is cut along K: park the fp32 partial sums, then the last quarter-warp to arrive adds
+        // the segments in K order.
+        float* mine = a.partial + (long long)it.slot_of(sg, sg.seg) * slot_floats;
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           uint32_t g[16], up[16];
           tmem_ld_16(taddr + c0, g);
@@ -501,21 +612,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         __threadfence();
         __syncwarp();
         int old = 0;
-        if (lane == 0) old = atomicAdd(&a.counters[tile_mb * 4 + wq], 1);
+        if (lane == 0) old = atomicAdd(&a.counters[sg.unit * 4 + wq], 1);
         old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == split - 1) {
+        if (old == sg.nseg - 1) {
           __threadfence();
-          const float* base = a.partial + (long long)tile_mb * split * slot_floats;
           // Eight token columns at a time: their loads are independent and issued together (a loop that
           // took one column per L2 round trip cost tens of microseconds on 64-column tiles); the sums
-          // still run over the splits in order s = 0, 1, ... for every column.
+          // still run over the segments in K order for every column.
           constexpr int kFix = 8;
           for (int n0 = 0; n0 < n_rows; n0 += kFix) {
             float v[kFix], w[kFix];
 #pragma unroll
             for (int j = 0; j < kFix; ++j) v[j] = w[j] = 0.f;
-            for (int s = 0; s < split; ++s) {
-              const float* p = base + s * slot_floats;
+            for (int s = 0; s < sg.nseg; ++s) {
+              const float* p = a.partial + (long long)it.slot_of(sg, s) * slot_floats;
               float pv[kFix], pw[kFix];
 #pragma unroll
               for (int j = 0; j < kFix; ++j) {
@@ -548,13 +658,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               }
             }
           }
-          if (lane == 0) a.counters[tile_mb * 4 + wq] = 0;
+          if (lane == 0) a.counters[sg.unit * 4 + wq] = 0;
           if (with_return) ok = enqueue_return(n_rows, row_start, mb);
         }
       }
       acc.advance(kAccStages);
       if (trace && warp == 4 && lane == 0) trace[5] = global_timer_ns();
     }
+    if (it.bad_tile && warp == 4 && lane == 0) report_status(a.status, kBadArgument, 7, blockIdx.x, 0);
     if (with_return) enqueue_return(-1, 0, 0);  // tell the return warp that nothing more will come
   } else {
     // ------------------------------------------------------------------ return warps (fused owner reduce + push)
@@ -612,12 +723,16 @@ static EncodeTiledFn get_encode_fn() {
 template <bool kGateUp, int N_MAX, bool kReturn = false>
 static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStream_t stream) {
   using Cfg = GemmCfg<kGateUp, N_MAX>;
-  static bool configured = false;
+  // The shared-memory attribute belongs to (function, device): set it once per device this process drives.
+  static bool configured[kMaxDevices] = {};
   auto kern = grouped_gemm_kernel<kGateUp, N_MAX, kReturn>;
-  if (!configured) {
+  int dev = 0;
+  cudaError_t de = cudaGetDevice(&dev);
+  if (de != cudaSuccess) return (int)de;
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
   CUtensorMap tm, tb;
   memcpy(&tm, tmap, sizeof(tm));
@@ -717,7 +832,8 @@ constexpr size_t kStaticCounterBytes = (size_t)MF_STATIC_SCRATCH_MAX_COUNTERS * 
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes];
 
-constexpr int kMaxDevices = 64;
+// One host thread at a time per device is assumed for the first call (the table is written without a lock;
+// two threads racing here would both store the same address).
 static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 
 }  // namespace mf
@@ -760,6 +876,11 @@ extern "C" int mf_gemm_down_static_scratch(const void* tmap, const mf_gemm_args*
   a.counters = reinterpret_cast<int*>(base + kStaticPartialBytes);
   a.max_split_slots = MF_STATIC_SCRATCH_MAX_SLOTS;
   a.b_tmap = nullptr;  // this entry always gathers the token rows
+  // What the kernel may index, for its own check of the plan words (they live in device memory and can
+  // disagree with max_tiles / split): the whole partial area, the counters cleared above, the declared tiles.
+  a.partial_floats = (long long)(kStaticPartialBytes / sizeof(float));
+  a.n_counters = (int)counters;
+  a.max_tiles = max_tiles;
   CUtensorMap tm;
   memcpy(&tm, tmap, sizeof(tm));
   grouped_gemm_kernel<false, kStaticNMax>

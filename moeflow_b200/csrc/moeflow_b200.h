@@ -14,8 +14,8 @@ typedef void* mf_stream_t;
 // ---- plan words written by mf_expert_meta and read by the grouped GEMMs -------------------------
 enum {
   MF_PLAN_N_TILES = 0,    // number of (expert, row range) token tiles
-  MF_PLAN_SPLIT1 = 1,     // K split of the gate/up GEMM
-  MF_PLAN_SPLIT2 = 2,     // K split of the down GEMM
+  MF_PLAN_SPLIT1 = 1,     // K cut of the gate/up GEMM: 1, 2, 4 or 8 equal segments per unit, or 0 = stream-K
+  MF_PLAN_SPLIT2 = 2,     // K cut of the down GEMM
   MF_PLAN_N_ENTRIES = 3,  // valid (row, slot) entries = offsets[L]
   MF_PLAN_SLOT_COLS = 4,  // token columns per split-K partial slot (multiple of 16; 0 = the kernel's n_max)
   MF_PLAN_VALID_ROWS = 5, // received rows with at least one hit on this rank
@@ -71,6 +71,11 @@ typedef struct {
   // b_base + n * b_pitch): token tiles are then fetched by TMA, one bulk copy per pipeline stage, instead of
   // being gathered 16 bytes at a time.  Rows past a tile's end are fetched too and ignored.
   const void* b_tmap;
+  // Capacities the kernel checks the plan against before it stores anything (0 = not checked).  A plan whose
+  // tile count or K cut needs more than this is refused on the device: status word kBadArgument, no store.
+  long long partial_floats;  // floats in `partial`
+  int n_counters;            // ints in `counters`
+  int max_tiles;             // entries in tile_e / tile_s / tile_n
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
@@ -102,6 +107,10 @@ int mf_gemm_smem_bytes(int gate_up, int n_max);
 //    of the plan word args->split_word (1, 2, 4 or 8).  The call is refused with a negative code, and
 //    nothing is launched, when max_tiles * m_blocks * split exceeds MF_STATIC_SCRATCH_MAX_SLOTS (-20)
 //    or max_tiles * m_blocks * 4 exceeds MF_STATIC_SCRATCH_MAX_COUNTERS (-21).
+//  * The plan itself lives in device memory, so the kernel checks it again before it stores anything:
+//    a tile count above `max_tiles`, a K cut whose partial tiles do not fit the array, or a tile wider
+//    than 64 rows makes the kernel report "bad argument" in args->status and leave the output, the
+//    array and its neighbours untouched (a wide tile is skipped, the rest of the plan still runs).
 //  * It calls no cudaMalloc / cudaFree and no allocating library routine.  The scratch array
 //    (MF_STATIC_SCRATCH_MAX_SLOTS * 32 KiB + MF_STATIC_SCRATCH_MAX_COUNTERS * 4 bytes, about 4.1 MiB) is
 //    held by every GPU that loads the library until the process exits.
@@ -183,6 +192,9 @@ typedef struct {
   int n_ctas;
   int* cta_hist;
   int* acc;
+  // 1: GEMMs with fewer than 8 units per CTA get the stream-K cut (plan word 0) when the scratch holds two
+  // partial tiles per CTA; 0: always a K split from mf_plan_split.
+  int stream_k;
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 // The K-split rule of the metadata kernels, callable on the host (no device needed): the split in {1,2,4,8}

@@ -3,7 +3,9 @@
 // owner_reduce_push: for every received row (s, t) that is valid,
 //     partial = bf16( sum_{k = 0..K-1, inv[row*K+k] >= 0} fp32(y[inv[row*K+k]]) )        (+0.0 start)
 // is stored straight into the source rank's combine buffer ret_recv_s[this rank, t] through the peer
-// mapping; the last CTA then publishes the epoch in every source's return flag [this rank].
+// mapping; every CTA (one per received row) then fences once and adds one to the source's return flag
+// [this rank].  The flags count arrivals: a forward brings C of them per owner, the combine waits for
+// epoch * C.
 // `y` already holds bf16(routing weight * fp32 accumulator) from the down GEMM.
 //
 // combine: waits (bounded) for the return flags of all R owners, then
@@ -44,12 +46,15 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   const int s = row / a.C, t = row - s * a.C;
   const int tid = threadIdx.x;
   grid_dep_launch();
-  grid_dep_wait();  // the down GEMM has completed: y is final
+  // The valid flag and the inverse map were final before the GEMMs started (this grid can only be resident
+  // once the down GEMM is, which follows the gate/up GEMM's wait for the metadata pass), so they are fetched
+  // ahead of the wait: two dependent cold loads less after the GEMM's last store.
   const int* meta = reinterpret_cast<const int*>(static_cast<const uint8_t*>(a.recv) + (size_t)row * a.pitch +
                                                  (size_t)a.H * 2);
-  const bool valid = meta[a.valid_word] != 0;
+  const bool valid = __ldcg(meta + a.valid_word) != 0;
+  if (valid && tid < a.K) s_pos[tid] = __ldcg(a.inv + (size_t)row * a.K + tid);
+  grid_dep_wait();  // the down GEMM has completed: y is final
   if (valid) {
-    if (tid < a.K) s_pos[tid] = a.inv[(size_t)row * a.K + tid];
     __syncthreads();
     const int chunks = a.H / 8;
     const uint4* y = static_cast<const uint4*>(a.y);
@@ -75,31 +80,33 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
     }
   }
   // The barrier orders every thread's stores before thread 0's fence, which is cumulative: one system
-  // fence per CTA instead of one per thread.
+  // fence per CTA instead of one per thread; then this row's arrival at its source rank.
   __syncthreads();
   if (tid == 0) {
     __threadfence_system();
-    const unsigned done = atomicAdd(a.done_counter, 1u);
-    if (done == gridDim.x - 1) {
-      *a.done_counter = 0u;
-      publish_flags(a.peer_flag, a.R, a.rank, *a.epoch);
-    }
+    red_add_relaxed_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[s]) + a.rank, 1u);
   }
 }
 
 __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_args a) {
+  __shared__ unsigned char s_hit[256];
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
+  // hit[t, :] was written by this rank's dispatch kernel: pull its line into L2 ahead of the wait (a hint only,
+  // the values are read after the wait), so that the read below does not go to DRAM.
+  if (tid == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.hit + (size_t)t * a.R));
   grid_dep_wait();
+  if (tid < a.R) s_hit[tid] = __ldcg(a.hit + (size_t)t * a.R + tid);
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
+  // counting flags: every owner adds one per received row of this rank (C of them) in every forward
   if (a.flags != nullptr && tid < a.R) {
-    if (!wait_flag_ge(a.flags + tid, epoch, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);
+    if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)a.C, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);
   }
   __syncthreads();
   const int chunks = a.H / 8;
   const uint4* ret = static_cast<const uint4*>(a.ret);
   uint4* out = static_cast<uint4*>(a.out) + (size_t)t * chunks;
-  const unsigned char* hit = a.hit + (size_t)t * a.R;
+  const unsigned char* hit = s_hit;
   for (int c = tid; c < chunks; c += kRowThreads) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (!a.ring) {
@@ -172,28 +179,30 @@ int mf_peer_ping(const unsigned long long* peer_words, unsigned* local_words, in
 // -------------------------------------------------------------------------------------------------
 namespace mf {
 __global__ void __launch_bounds__(kRowThreads)
-expert_prepare_kernel(const uint8_t* __restrict__ rows, long long pitch, int H, int K, int rank_offset, int filler,
-                      uint4* __restrict__ hidden, int* __restrict__ ids32, long long* __restrict__ ids64,
-                      float* __restrict__ weights) {
+expert_prepare_kernel(const uint8_t* rows, long long pitch, int H, int K, int rank_offset, int filler, uint4* hidden,
+                      int* ids32, long long* ids64, float* weights) {
+  // No __restrict__ / read-only loads here: this kernel may become resident (programmatic launch) before its
+  // predecessors have written the rows, and loads through the non-coherent path are only defined for data that
+  // does not change during the kernel's lifetime.  Every input produced earlier in the stream is read from L2.
   grid_dep_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const uint8_t* row = rows + (size_t)r * pitch;
   const int* meta = reinterpret_cast<const int*>(row + (size_t)H * 2);
-  const bool valid = meta[2 * K] != 0;
+  const bool valid = __ldcg(meta + 2 * K) != 0;
   if (tid < K) {
-    const int local = meta[tid];
+    const int local = __ldcg(meta + tid);
     const bool live = valid && local >= 0;
     const int gid = live ? local + rank_offset : filler;
     if (ids32) ids32[(size_t)r * K + tid] = gid;
     if (ids64) ids64[(size_t)r * K + tid] = gid;
-    weights[(size_t)r * K + tid] = live ? __int_as_float(meta[K + tid]) : 0.f;
+    weights[(size_t)r * K + tid] = live ? __int_as_float(__ldcg(meta + K + tid)) : 0.f;
   }
   const int chunks = H / 8;
   const uint4* src = reinterpret_cast<const uint4*>(row);
   uint4* dst = hidden + (size_t)r * chunks;
   // Rows that are not valid may hold stale payload (even NaN): copy them as they are; their slots all
   // point at the filler expert with weight 0, so nothing of them reaches an output.
-  for (int c = tid; c < chunks; c += kRowThreads) dst[c] = src[c];
+  for (int c = tid; c < chunks; c += kRowThreads) dst[c] = __ldcg(src + c);
 }
 }  // namespace mf
 
@@ -215,18 +224,23 @@ extern "C" int mf_expert_prepare(const void* rows, long long pitch, int n_rows, 
 // -------------------------------------------------------------------------------------------------
 namespace mf {
 __global__ void __launch_bounds__(kRowThreads)
-permute_rows_kernel(const uint8_t* __restrict__ recv, long long pitch, const int* __restrict__ entry_row,
-                    const int* __restrict__ plan, uint4* __restrict__ xg, int H, int n_rows) {
+permute_rows_kernel(const uint8_t* recv, long long pitch, const int* entry_row, const int* plan, uint4* xg, int H,
+                    int n_rows) {
+  // The pointers are deliberately not __restrict__ and every input is read with ld.global.cg: this kernel is
+  // resident (programmatic launch) while the dispatch and metadata kernels are still writing recv, entry_row
+  // and the plan, and a load through the non-coherent read-only path (which the compiler may pick for
+  // const __restrict__ data) is only defined for memory that does not change during the kernel's lifetime.
+  // With such loads the copy returned rows of an earlier forward on the same addresses.
   grid_dep_launch();
   grid_dep_wait();  // the metadata pass has completed: entry_row and the plan are final
-  const int n_entries = plan[MF_PLAN_N_ENTRIES];
+  const int n_entries = __ldcg(plan + MF_PLAN_N_ENTRIES);
   const int chunks = H / 8;
   for (int pos = blockIdx.x; pos < n_entries; pos += gridDim.x) {
-    const int r = entry_row[pos];
+    const int r = __ldcg(entry_row + pos);
     if (r < 0 || r >= n_rows) continue;  // never taken for a consistent layout; keeps a bad index from being followed
     const uint4* src = reinterpret_cast<const uint4*>(recv + (size_t)r * pitch);
     uint4* dst = xg + (size_t)pos * chunks;
-    for (int c = threadIdx.x; c < chunks; c += kRowThreads) dst[c] = src[c];
+    for (int c = threadIdx.x; c < chunks; c += kRowThreads) dst[c] = __ldcg(src + c);
   }
 }
 }  // namespace mf

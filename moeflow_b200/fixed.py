@@ -477,7 +477,7 @@ class FixedEPLayer:
             n_counters2=self._counters2.numel(), block_m=self.block_m, max_tiles=self.max_tiles, m_blocks1=mb1,
             k_blocks1=H // 64, m_blocks2=mb2, k_blocks2=I // 64, n_sms=self.n_sms,
             max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
-            partial_floats=partial_floats,
+            partial_floats=partial_floats, stream_k=int(self.gemm_kwargs.get("stream_k", 1)),
         )
         # Metadata: one CTA for decode sizes; for prefill sizes (many received rows) the counting sort is
         # split over several CTAs in two chained launches.  Same result either way.
@@ -498,17 +498,19 @@ class FixedEPLayer:
             tile_e=self.tile_e.data_ptr(), tile_s=self.tile_s.data_ptr(), tile_n=self.tile_n.data_ptr(),
             plan=self.plan.data_ptr(), partial=self._partial.data_ptr(), max_split_slots=self.max_split_slots,
             limit=float(limit), round_h=int(self.gemm_kwargs.get("round_h", 0)), status=self.status.data_ptr(),
-            wait_ns=self.wait_ns,
+            wait_ns=self.wait_ns, partial_floats=partial_floats, max_tiles=self.max_tiles,
         )
         self._a_gemm1 = S.GemmArgs(
             b_base=self._recv_store.data_ptr(), b_pitch=self.pitch * 2, b_index=self.entry_row.data_ptr(),
             split_word=S.PLAN_SPLIT1, m_blocks=mb1, k_blocks=H // 64, rows_per_expert=2 * I, up_row_offset=I,
-            out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=self._counters1.data_ptr(), **common,
+            out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=self._counters1.data_ptr(),
+            n_counters=self._counters1.numel(), **common,
         )
         self._a_gemm2 = S.GemmArgs(
             b_base=self.act.data_ptr(), b_pitch=I * 2, b_index=None, split_word=S.PLAN_SPLIT2, m_blocks=mb2,
             k_blocks=I // 64, rows_per_expert=H, up_row_offset=0, out=self.y.data_ptr(), out_pitch=H,
-            row_scale=self.entry_w.data_ptr(), counters=self._counters2.data_ptr(), **common,
+            row_scale=self.entry_w.data_ptr(), counters=self._counters2.data_ptr(),
+            n_counters=self._counters2.numel(), **common,
         )
         # The down GEMM reads its token operand (act, contiguous in expert-major order) by TMA, one bulk copy
         # per pipeline stage; gemm_kwargs b_tma=False falls back to the 16-byte gather the gate/up GEMM uses.
@@ -615,15 +617,16 @@ class FixedEPLayer:
         f["as"] = torch.zeros(N, I // 128, dtype=torch.float32, device=dev)
         g1, g2 = self._a_gemm1, self._a_gemm2
         common = dict(tile_e=g1.tile_e, tile_s=g1.tile_s, tile_n=g1.tile_n, plan=g1.plan, partial=g1.partial,
-                      max_split_slots=g1.max_split_slots, limit=g1.limit, round_h=0, status=g1.status, wait_ns=g1.wait_ns)
+                      max_split_slots=g1.max_split_slots, limit=g1.limit, round_h=0, status=g1.status, wait_ns=g1.wait_ns,
+                      partial_floats=g1.partial_floats, max_tiles=g1.max_tiles)
         f["a1"] = _lib.GemmArgs(b_base=f["xq"].data_ptr(), b_pitch=H, b_index=self.entry_row.data_ptr(),
                                 split_word=_lib.PLAN_SPLIT1, m_blocks=I // 128, k_blocks=H // 128, rows_per_expert=2 * I,
                                 up_row_offset=I, out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=g1.counters,
-                                w_scale=f["s13"].data_ptr(), b_scale=f["xs"].data_ptr(), b_scale_pitch=H // 128, **common)
+                                n_counters=g1.n_counters, w_scale=f["s13"].data_ptr(), b_scale=f["xs"].data_ptr(), b_scale_pitch=H // 128, **common)
         f["a2"] = _lib.GemmArgs(b_base=f["aq"].data_ptr(), b_pitch=I, b_index=None, split_word=_lib.PLAN_SPLIT2,
                                 m_blocks=H // 128, k_blocks=I // 128, rows_per_expert=H, up_row_offset=0,
                                 out=self.y.data_ptr(), out_pitch=H, row_scale=self.entry_w.data_ptr(), counters=g2.counters,
-                                w_scale=f["s2"].data_ptr(), b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128, **common)
+                                n_counters=g2.n_counters, w_scale=f["s2"].data_ptr(), b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128, **common)
         self._fp8 = f
         self._tmap13, self._tmap2 = f["tm13"], f["tm2"]
 

@@ -69,29 +69,23 @@ class SharedExpert:
         self.n_sms = sm_count(dev.index or 0)
         n_tiles = (capacity + block_m - 1) // block_m
 
-        def pick_split(m_blocks: int, k_blocks: int) -> int:
-            # one expert has few weight blocks: split K so that the weight stream covers the SMs
-            best = 1
-            for s in (2, 4, 8):
-                if k_blocks % s == 0 and k_blocks // s >= 2 and n_tiles * m_blocks * s <= 2 * self.n_sms:
-                    best = s
-            return best
-
-        s1 = pick_split(self.inter // 128, self.hidden // 64)
-        s2 = pick_split(self.hidden // 128, self.inter // 64)
-        self.tp = plan_from_offsets([0, capacity], block_m, dev, split1=s1, split2=s2)
+        # One expert has few weight blocks (12 and 32 at the GLM shape): the stream-K cut (plan word 0) lays the
+        # K steps of all units end to end and gives every SM the same share of the weight stream.
+        self.tp = plan_from_offsets([0, capacity], block_m, dev, split1=0, split2=0)
         self.act = torch.zeros(capacity, self.inter, dtype=torch.bfloat16, device=dev)
         self.out = torch.zeros(capacity, self.hidden, dtype=torch.bfloat16, device=dev)
         self.status = torch.zeros(1, dtype=torch.int64, device=dev)
         self._x = torch.zeros(capacity, self.hidden, dtype=torch.bfloat16, device=dev)
         self._tm13 = make_weight_tmap(self.w13.view(1, 2 * self.inter, self.hidden))
         self._tm2 = make_weight_tmap(self.w2.view(1, self.hidden, self.inter))
-        slots = n_tiles * max(self.inter // 128 * s1, self.hidden // 128 * s2)
+        slots = 2 * self.n_sms  # stream-K: two partial tiles per CTA
         self._scratch = torch.zeros(slots * 2 * block_m * 128, dtype=torch.float32, device=dev)
         self._counters = torch.zeros(self.tp.n_tiles * max(self.inter, self.hidden) // 128 * 4, dtype=torch.int32, device=dev)
         common = dict(tile_e=self.tp.tile_e.data_ptr(), tile_s=self.tp.tile_s.data_ptr(), tile_n=self.tp.tile_n.data_ptr(),
                       plan=self.tp.plan.data_ptr(), partial=self._scratch.data_ptr(), counters=self._counters.data_ptr(),
-                      max_split_slots=slots, status=self.status.data_ptr(), wait_ns=2_000_000_000)
+                      max_split_slots=slots, status=self.status.data_ptr(), wait_ns=2_000_000_000,
+                      partial_floats=self._scratch.numel(), n_counters=self._counters.numel(),
+                      max_tiles=self.tp.tile_e.numel())
         self._a1 = _lib.GemmArgs(b_base=self._x.data_ptr(), b_pitch=self.hidden * 2, b_index=None, split_word=_lib.PLAN_SPLIT1,
                                  m_blocks=self.inter // 128, k_blocks=self.hidden // 64, rows_per_expert=2 * self.inter,
                                  up_row_offset=self.inter, out=self.act.data_ptr(), out_pitch=self.inter, row_scale=None,

@@ -70,6 +70,9 @@ class GemmArgs(C.Structure):
         ("ret_C", C.c_int),
         ("ret_K", C.c_int),
         ("b_tmap", C.c_void_p),
+        ("partial_floats", C.c_longlong),
+        ("n_counters", C.c_int),
+        ("max_tiles", C.c_int),
     ]
 
 
@@ -145,6 +148,7 @@ class MetaArgs(C.Structure):
         ("n_ctas", C.c_int),
         ("cta_hist", C.c_void_p),
         ("acc", C.c_void_p),
+        ("stream_k", C.c_int),
     ]
 
 

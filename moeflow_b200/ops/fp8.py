@@ -70,7 +70,8 @@ def _gemm_fp8(gate_up: bool, xq, xs, wq, ws, tp: TilePlan, out, row_index, row_s
     m_blocks = inter // 128
     word = _lib.PLAN_SPLIT1 if gate_up else _lib.PLAN_SPLIT2
     tp.plan[word] = split
-    partial, counters, slots = _scratch(tp, m_blocks, split, dev)
+    grid = grid or sm_count(dev.index or 0)
+    partial, counters, slots = _scratch(tp, m_blocks, split, dev, grid)
     status = status if status is not None else torch.zeros(1, dtype=torch.int64, device=dev)
     args = _lib.GemmArgs(
         b_base=xq.data_ptr(), b_pitch=xq.stride(0), b_index=_lib.ptr(row_index), tile_e=tp.tile_e.data_ptr(),
@@ -80,7 +81,6 @@ def _gemm_fp8(gate_up: bool, xq, xs, wq, ws, tp: TilePlan, out, row_index, row_s
         counters=counters.data_ptr(), max_split_slots=slots, limit=float(limit) if limit is not None else 0.0, round_h=0,
         status=status.data_ptr(), wait_ns=wait_ns, w_scale=ws.data_ptr(), b_scale=xs.data_ptr(), b_scale_pitch=xs.stride(0),
     )
-    grid = grid or sm_count(dev.index or 0)
     fn = _lib.lib().mf_gemm_gate_up_fp8 if gate_up else _lib.lib().mf_gemm_down_fp8
     _lib.check(fn(tmap, C.byref(args), tp.block_m, grid, _lib.stream_ptr()), "fp8 gemm")
     out._keep = (wq, ws, partial, counters, status, xq, xs, row_index, row_scale)

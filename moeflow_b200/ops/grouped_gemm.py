@@ -55,9 +55,11 @@ def plan_from_offsets(offsets, block_m: int, device, split1: int = 1, split2: in
     )
 
 
-def _scratch(tp: TilePlan, m_blocks: int, split: int, device):
-    slots = max(1, tp.n_tiles * m_blocks * split)
-    partial = torch.empty(slots * 2 * tp.block_m * 128 if split > 1 else 1, dtype=torch.float32, device=device)
+def _scratch(tp: TilePlan, m_blocks: int, split: int, device, grid: int):
+    """Partial-sum tiles and arrival counters for a K cut: ``split`` segments per unit, or (``split == 0``,
+    stream-K) two tiles per CTA."""
+    slots = max(1, 2 * grid if split == 0 else tp.n_tiles * m_blocks * split)
+    partial = torch.empty(slots * 2 * tp.block_m * 128 if split != 1 else 1, dtype=torch.float32, device=device)
     counters = torch.zeros(max(1, tp.n_tiles) * m_blocks * 4, dtype=torch.int32, device=device)
     return partial, counters, slots
 
@@ -73,8 +75,12 @@ def gate_up_swiglu(
     status: torch.Tensor | None = None,
     wait_ns: int = 2_000_000_000,
     grid: int | None = None,
+    b_tma: bool = False,
 ) -> torch.Tensor:
-    """``act[n] = silu(min(x[i_n] . Wg^T, lim)) * clamp(x[i_n] . Wu^T, +-lim)`` per expert segment."""
+    """``act[n] = silu(min(x[i_n] . Wg^T, lim)) * clamp(x[i_n] . Wu^T, +-lim)`` per expert segment.
+
+    ``b_tma`` (only without ``row_index``, contiguous ``x``): fetch the token tiles by TMA instead of the
+    16-byte gather."""
     n_exp, two_i, hidden = w13.shape
     inter = two_i // 2
     if x.dtype != torch.bfloat16 or w13.dtype != torch.bfloat16:
@@ -88,7 +94,8 @@ def gate_up_swiglu(
     tmap = make_weight_tmap(w13)
     act = torch.zeros(max(tp.n_entries, 1), inter, dtype=torch.bfloat16, device=dev)
     tp.plan[_lib.PLAN_SPLIT1] = split
-    partial, counters, slots = _scratch(tp, inter // 128, split, dev)
+    grid = grid or sm_count(dev.index or 0)
+    partial, counters, slots = _scratch(tp, inter // 128, split, dev, grid)
     status = status if status is not None else torch.zeros(1, dtype=torch.int64, device=dev)
     args = _lib.GemmArgs(
         b_base=x.data_ptr(), b_pitch=x.stride(0) * 2, b_index=_lib.ptr(row_index), tile_e=tp.tile_e.data_ptr(),
@@ -96,9 +103,18 @@ def gate_up_swiglu(
         m_blocks=inter // 128, k_blocks=hidden // 64, rows_per_expert=two_i, up_row_offset=inter, out=act.data_ptr(),
         out_pitch=inter, row_scale=None, partial=partial.data_ptr(), counters=counters.data_ptr(),
         max_split_slots=slots, limit=float(limit) if limit is not None else 0.0, round_h=int(round_h),
-        status=status.data_ptr(), wait_ns=wait_ns,
+        status=status.data_ptr(), wait_ns=wait_ns, partial_floats=partial.numel(), n_counters=counters.numel(),
+        max_tiles=tp.tile_e.numel(),
     )
-    grid = grid or sm_count(dev.index or 0)
+    tmap_b = None
+    if b_tma:
+        if row_index is not None or not x.is_contiguous():
+            raise ValueError("token tiles by TMA need contiguous rows and no row index")
+        if x.shape[0] < tp.block_m:  # the tensor map needs at least one box of rows
+            x = torch.cat([x, x.new_zeros(tp.block_m - x.shape[0], hidden)])
+            args.b_base = x.data_ptr()
+        tmap_b = make_tile_tmap(x, tp.block_m)
+        args.b_tmap = C.addressof(tmap_b)
     _lib.check(_lib.lib().mf_gemm_gate_up(tmap, C.byref(args), tp.block_m, grid, _lib.stream_ptr()), "gate/up gemm")
     act._keep = (w13, partial, counters, status, row_index, x)
     return act[: tp.n_entries]
@@ -131,20 +147,21 @@ def down_proj(
     tmap = make_weight_tmap(w2)
     y = torch.zeros(max(tp.n_entries, 1), hidden, dtype=torch.bfloat16, device=dev)
     tp.plan[_lib.PLAN_SPLIT2] = split
-    partial, counters, slots = _scratch(tp, hidden // 128, split, dev)
+    grid = grid or sm_count(dev.index or 0)
+    partial, counters, slots = _scratch(tp, hidden // 128, split, dev, grid)
     status = status if status is not None else torch.zeros(1, dtype=torch.int64, device=dev)
     args = _lib.GemmArgs(
         b_base=act.data_ptr(), b_pitch=inter * 2, b_index=None, tile_e=tp.tile_e.data_ptr(), tile_s=tp.tile_s.data_ptr(),
         tile_n=tp.tile_n.data_ptr(), plan=tp.plan.data_ptr(), split_word=_lib.PLAN_SPLIT2, m_blocks=hidden // 128,
         k_blocks=inter // 64, rows_per_expert=hidden, up_row_offset=0, out=y.data_ptr(), out_pitch=hidden,
         row_scale=_lib.ptr(row_scale), partial=partial.data_ptr(), counters=counters.data_ptr(), max_split_slots=slots,
-        limit=0.0, round_h=0, status=status.data_ptr(), wait_ns=wait_ns,
+        limit=0.0, round_h=0, status=status.data_ptr(), wait_ns=wait_ns, partial_floats=partial.numel(),
+        n_counters=counters.numel(), max_tiles=tp.tile_e.numel(),
     )
     tmap_b = None
     if b_tma:
         tmap_b = make_tile_tmap(act, tp.block_m)
         args.b_tmap = C.addressof(tmap_b)
-    grid = grid or sm_count(dev.index or 0)
     _lib.check(_lib.lib().mf_gemm_down(tmap, C.byref(args), tp.block_m, grid, _lib.stream_ptr()), "down gemm")
     y._keep = (w2, partial, counters, status, row_scale, act)
     return y[: tp.n_entries]

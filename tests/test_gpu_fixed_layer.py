@@ -243,12 +243,16 @@ def test_ring_combine_rounding_witness():
 
 @pytest.mark.parametrize("world", [1, 2])
 def test_graph_replay_with_changing_inputs(world):
-    """Capture each rank's stages in CUDA graphs, replay with new inputs and valid prefixes."""
+    """Capture each rank's stages in CUDA graphs and replay them 1000 times with new inputs and valid prefixes.
+    Every replay is compared bit for bit with an eager forward of a second set of cuda-backend layers on the
+    same inputs (same kernels, so the bits must match: a replay that read one stale row would not), every
+    50th also with the torch twin within the GEMM tolerance; padding rows must be exactly zero."""
     cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=2)
     cap = 8
     w13, w2 = make_weights(cfg, 0, device="cuda")
     bias = make_bias(cfg, 1, device="cuda")
     cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    eager = _layers(cfg, world, cap, w13, w2, "cuda")
     tw = _layers(cfg, world, cap, w13, w2, "torch")
     xs = [torch.zeros(cap, cfg.hidden_size, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
     lgs = [torch.zeros(cap, cfg.n_routed_experts, device="cuda") for _ in range(world)]
@@ -276,23 +280,77 @@ def test_graph_replay_with_changing_inputs(world):
             g_comb.append(g)
     torch.cuda.synchronize()
     gen = torch.Generator().manual_seed(0)
-    for it in range(50):
+    pool = [(make_hidden(cap, cfg, 1000 + i, device="cuda"), make_logits(cap, cfg, 2000 + i, device="cuda")) for i in range(64)]
+    for it in range(1000):
         for r in range(world):
-            xs[r].copy_(make_hidden(cap, cfg, 1000 + it * 7 + r))
-            lgs[r].copy_(make_logits(cap, cfg, 2000 + it * 7 + r))
+            x, lg = pool[int(torch.randint(0, len(pool), (1,), generator=gen))]
+            xs[r].copy_(x)
+            lgs[r].copy_(lg)
             nvs[r].fill_(int(torch.randint(0, cap + 1, (1,), generator=gen)))
         for g in g_pack + g_exp + g_comb:
             g.replay()
-        ref = simulate_fixed(tw, xs, lgs, bias, nvs)
+        want = simulate_fixed(eager, xs, lgs, bias, nvs)
         torch.cuda.synchronize()
         for r in range(world):
-            _ok(cu[r])
-            n = int(nvs[r])
-            assert cu[r].out[n:].abs().sum() == 0
-            if n:
-                err = normwise_rel_err(cu[r].out[:n], ref[r][:n].float())
-                assert err < 4 * 2.0**-8, (it, r, err)
+            assert bitwise_equal(cu[r].out, want[r]), (it, r)
+        if it % 50 == 0 or it == 999:
+            ref = simulate_fixed(tw, xs, lgs, bias, nvs)
+            torch.cuda.synchronize()
+            for r in range(world):
+                _ok(cu[r])
+                n = int(nvs[r])
+                assert cu[r].out[n:].abs().sum() == 0
+                if n:
+                    err = normwise_rel_err(cu[r].out[:n], ref[r][:n].float())
+                    assert err < 4 * 2.0**-8, (it, r, err)
     del g_pack, g_exp, g_comb
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_dispatch_under_1000_graph_replays_equals_the_twin_byte_for_byte(world):
+    """The dispatch kernel (routing + packing + peer stores) captured once and replayed 1000 times with changing
+    routes and valid prefixes: the whole receive buffer of every rank, stale padding rows included, equals the
+    torch twin's (pack + exchange) byte for byte after every replay."""
+    cfg = replace(SMALL_GPU, n_routed_experts=16, top_k=4)
+    cap = 8
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    cu = _layers(cfg, world, cap, w13, w2, "cuda", gemm_kwargs={"skip_payload": 0})
+    tw = _layers(cfg, world, cap, w13, w2, "torch")
+    xs = [torch.zeros(cap, cfg.hidden_size, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    lgs = [torch.zeros(cap, cfg.n_routed_experts, device="cuda") for _ in range(world)]
+    nvs = [torch.full((), cap, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for ly, x, lg, nv in zip(cu, xs, lgs, nvs):
+        ly.stage_pack(x, lg, bias, nv)
+    torch.cuda.synchronize()
+    graphs = []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for r, ly in enumerate(cu):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ly.stage_pack(xs[r], lgs[r], bias, nvs[r])
+            graphs.append(g)
+    torch.cuda.synchronize()
+    gen = torch.Generator().manual_seed(5)
+    pool = [(make_hidden(cap, cfg, 3000 + i, device="cuda"), make_logits(cap, cfg, 4000 + i, device="cuda")) for i in range(64)]
+    for it in range(1000):
+        for r in range(world):
+            x, lg = pool[int(torch.randint(0, len(pool), (1,), generator=gen))]
+            xs[r].copy_(x)
+            lgs[r].copy_(lg)
+            nvs[r].fill_(int(torch.randint(0, cap + 1, (1,), generator=gen)))
+        for g in graphs:
+            g.replay()
+        hits_t = [ly.stage_pack(x, lg, bias, nv) for ly, x, lg, nv in zip(tw, xs, lgs, nvs)]
+        for d in range(world):
+            for s in range(world):
+                tw[d]._recv_store[s].copy_(tw[s]._send_store[d])
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(cu[r].hit.bool(), hits_t[r].bool()), it
+            assert bitwise_equal(cu[r].recv.contiguous(), tw[r].recv.contiguous()), (it, r)
+    del graphs
 
 
 @pytest.mark.parametrize("ids_dtype", [torch.int32, torch.int64])

@@ -57,15 +57,20 @@ CASES = [
     ([70, 2, 130], 512, 128, 64),  # experts longer than one tile
     ([5, 9], 512, 256, 32),
     ([100, 20], 512, 256, 128),
+    ([128], 256, 128, 128),  # one full 128-row tile: UMMA N = 128, both 128-column accumulators of a stage
+    ([300, 5, 129], 512, 256, 128),  # experts spanning several 128-row tiles, a one-row remainder
+    ([128, 128, 64], 256, 128, 128),
 ]
 
 
 @pytest.mark.parametrize("counts,hidden,inter,block_m", CASES)
-@pytest.mark.parametrize("split", [1, 2, 4])
+@pytest.mark.parametrize("split", [0, 1, 2, 4])
 def test_gate_up_and_down(counts, hidden, inter, block_m, split):
+    """``split`` 1, 2, 4: equal K segments per unit; 0: the stream-K cut (every CTA one contiguous share of all
+    K steps, units cut at CTA boundaries)."""
     from moeflow_b200.ops.grouped_gemm import down_proj, gate_up_swiglu, plan_from_offsets
 
-    if (inter // 64) % split:
+    if split and (inter // 64) % split:
         pytest.skip("split does not divide the K blocks of the down GEMM")
     w13, w2, x, row_index, offsets, scale = _problem(counts, hidden, inter, seed=len(counts) + hidden)
     n = offsets[-1]
@@ -108,12 +113,13 @@ def test_clamp_is_exercised_and_identity_rows():
     assert normwise_rel_err(act_r, ref_r) < 4 * 2.0**-8
 
 
-def test_split_k_is_deterministic():
+@pytest.mark.parametrize("split", [4, 0])
+def test_split_k_is_deterministic(split):
     from moeflow_b200.ops.grouped_gemm import gate_up_swiglu, plan_from_offsets
 
     w13, _, x, row_index, offsets, _ = _problem([9, 30, 4], 1024, 256, seed=9)
     tp = plan_from_offsets(offsets, 64, x.device)
-    runs = [gate_up_swiglu(x, w13, tp, row_index=row_index[: offsets[-1]], split=4).clone() for _ in range(5)]
+    runs = [gate_up_swiglu(x, w13, tp, row_index=row_index[: offsets[-1]], split=split).clone() for _ in range(5)]
     torch.cuda.synchronize()
     for r in runs[1:]:
         assert torch.equal(r.view(torch.int16), runs[0].view(torch.int16))
@@ -170,3 +176,65 @@ def test_down_proj_token_tiles_by_tma_equal_the_gather_bitwise(counts, block_m, 
     _status_ok(status)
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
     assert normwise_rel_err(a, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8
+
+
+@pytest.mark.parametrize("counts,hidden,inter,block_m,split", [([3, 0, 17, 5], 512, 256, 64, 1), ([70, 2, 130], 512, 128, 64, 2),
+                                                          ([128], 256, 128, 128, 1), ([300, 5, 129], 512, 256, 128, 1),
+                                                          ([127, 131, 3, 128], 256, 128, 128, 1), ([5, 9], 512, 256, 32, 4)])
+def test_gate_up_token_tiles_by_tma_equal_the_gather_bitwise_and_the_oracle(counts, hidden, inter, block_m, split):
+    """Gate/up GEMM with its token tiles fetched by TMA (contiguous rows) or gathered by cp.async: same bits,
+    and both within tolerance of fp32 PyTorch.  Includes full 128-row tiles."""
+    from moeflow_b200.ops.grouped_gemm import gate_up_swiglu, plan_from_offsets
+
+    w13, _, x, _, offsets, _ = _problem(counts, hidden, inter, seed=31)
+    n = offsets[-1]
+    x = x[:n].contiguous()
+    tp = plan_from_offsets(offsets, block_m, x.device)
+    status = torch.zeros(1, dtype=torch.int64, device=x.device)
+    ident = torch.arange(n, dtype=torch.int32, device=x.device)
+    a = gate_up_swiglu(x, w13, tp, limit=10.0, split=split, status=status, wait_ns=50_000_000, b_tma=True).clone()
+    b = gate_up_swiglu(x, w13, tp, row_index=ident, limit=10.0, split=split, status=status, wait_ns=50_000_000).clone()
+    torch.cuda.synchronize()
+    _status_ok(status)
+    ref = _ref_gate_up(x, ident, w13, offsets, 10.0)
+    assert normwise_rel_err(b, ref) < 4 * 2.0**-8, "gather"
+    assert normwise_rel_err(a, ref) < 4 * 2.0**-8, "tma"
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("grid", [1, 3, 7, 50, 148, 149, 300])
+@pytest.mark.parametrize("counts,hidden,inter,block_m", [([16, 64, 1, 0, 33], 1024, 384, 64), ([130], 512, 256, 128)])
+def test_stream_k_cut_for_any_number_of_ctas(grid, counts, hidden, inter, block_m):
+    """Stream-K with fewer CTAs than units, more CTAs than K steps, and shares that start or end exactly on
+    a unit boundary: same result (within tolerance of fp32 PyTorch) for every grid size."""
+    from moeflow_b200.ops.grouped_gemm import down_proj, gate_up_swiglu, plan_from_offsets
+
+    w13, w2, x, row_index, offsets, scale = _problem(counts, hidden, inter, seed=77)
+    n = offsets[-1]
+    tp = plan_from_offsets(offsets, block_m, x.device)
+    status = torch.zeros(1, dtype=torch.int64, device=x.device)
+    act = gate_up_swiglu(x, w13, tp, row_index=row_index[:n], split=0, status=status, wait_ns=50_000_000, grid=grid)
+    y = down_proj(act, w2, tp, row_scale=scale[:n], split=0, status=status, wait_ns=50_000_000, grid=grid)
+    torch.cuda.synchronize()
+    _status_ok(status)
+    assert normwise_rel_err(act, _ref_gate_up(x, row_index[:n], w13, offsets, 10.0)) < 4 * 2.0**-8
+    assert normwise_rel_err(y, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8
+
+
+def test_a_plan_that_does_not_fit_the_scratch_is_refused_on_the_device():
+    """The plan words live in device memory; the kernel compares them with the capacities in its arguments and
+    reports 'bad argument' without storing anything when they do not fit."""
+    from moeflow_b200.ops._lib import decode_status
+    from moeflow_b200.ops.grouped_gemm import down_proj, plan_from_offsets
+
+    _, w2, _, _, offsets, scale = _problem([40, 9], 512, 256, seed=3)
+    n = offsets[-1]
+    act = torch.randn(n, 256).bfloat16().cuda()
+    tp = plan_from_offsets(offsets, 64, act.device)
+    status = torch.zeros(1, dtype=torch.int64, device=act.device)
+    tp.plan[0] = 1000  # claims far more tiles than the tile arrays and counters hold
+    y = down_proj(act, w2, tp, row_scale=scale[:n], split=2, status=status, wait_ns=50_000_000)
+    torch.cuda.synchronize()
+    st = decode_status(int(status.item()))
+    assert st["code"] == 7, st
+    assert float(y.float().abs().sum()) == 0.0

@@ -48,3 +48,18 @@ def test_fused_layer_over_peer_memory(dist_name):
         pytest.skip("needs at least 2 GPUs")
     out = _launch(n, "fixed_peer_check.py", "--dist", dist_name, "--iters", "12", "--replays", "120")
     assert out["ok"], out
+
+
+def test_graph_gate_interleaved_capacities_shared_buffers_one_gpu():
+    """The 1000-replay gate (capacities 1, 8, 64, 128 side by side, two weight sets on one buffer set, bitwise
+    against an eager layer) on a single GPU: stale-buffer contamination between graphs needs no second rank."""
+    out = _launch(1, "fixed_graph_gate.py", "--replays", "1000", timeout=900)
+    assert out["ok"] and out["replays"] == 1000, out
+
+
+def test_graph_gate_interleaved_capacities_shared_buffers_over_peers():
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    out = _launch(n, "fixed_graph_gate.py", "--replays", "1000", timeout=900)
+    assert out["ok"] and out["replays"] == 1000, out

@@ -84,3 +84,37 @@ def test_sizes_beyond_the_static_array_are_refused():
     assert code in (-20, -21)
     code, _, _ = _static_scratch_call(act, w2, tp, scale, 3)
     assert code == -2
+
+
+def test_a_plan_word_larger_than_declared_is_refused_on_the_device_and_nothing_is_written():
+    """The caller declares ``max_tiles`` and ``split`` on the host, but the kernel reads the plan from device
+    memory.  When the plan holds more tiles than declared, or tiles wider than the 64 rows this entry point
+    supports, the kernel must report 'bad argument' and leave the output untouched instead of running past
+    the static array."""
+    from moeflow_b200.ops import _lib
+    from moeflow_b200.ops.grouped_gemm import plan_from_offsets
+
+    w2, act, scale, offsets = _problem([5, 0, 40, 9], 512, 256, 5)
+    tp = plan_from_offsets(offsets, 64, act.device)
+    true_tiles = tp.n_tiles
+    tp.plan[_lib.PLAN_N_TILES] = true_tiles + 400  # the lie: (tiles + 400) * 4 blocks * 4 splits would overrun the array
+    code, y, status = _static_scratch_call(act, w2, tp, scale, 4, max_tiles=true_tiles)
+    torch.cuda.synchronize()
+    assert code == 0  # the host-side check saw only the declared sizes
+    assert _lib.decode_status(int(status.item()))["code"] == 7
+    assert float(y.float().abs().sum()) == 0.0
+    # tiles of 128 rows in a kernel built for 64: skipped and reported, the 64-row tiles still computed
+    tp = plan_from_offsets(offsets, 64, act.device)
+    tp.tile_n[0] = 100
+    code, y, status = _static_scratch_call(act, w2, tp, scale, 2)
+    torch.cuda.synchronize()
+    assert code == 0 and _lib.decode_status(int(status.item()))["code"] == 7
+    # and a correct call afterwards works on the same array
+    tp = plan_from_offsets(offsets, 64, act.device)
+    from moeflow_b200.ops.grouped_gemm import down_proj
+
+    code, y, status = _static_scratch_call(act, w2, tp, scale, 2)
+    ref = down_proj(act, w2, tp, row_scale=scale, split=2)
+    torch.cuda.synchronize()
+    assert code == 0 and _lib.decode_status(int(status.item()))["code"] == 0
+    assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
