@@ -146,6 +146,10 @@ class ReferenceFixedBackend:
             raise RuntimeError("the reference is not installed under baseline/_ref")
         if str(root) not in sys.path:
             sys.path.insert(0, str(root))
+        loaded = sys.modules.get("moeflow")
+        if loaded is not None and not str(getattr(loaded, "__file__", "")).startswith(str(root)):
+            raise RuntimeError("the name 'moeflow' is already bound to this framework's import alias in this process; "
+                               "run the reference arm in a process that has not imported it")
         from moeflow.config import MoEConfig as RefConfig  # type: ignore
         from moeflow.fixed import FixedEPLayer as RefLayer  # type: ignore
 

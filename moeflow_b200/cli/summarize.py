@@ -96,7 +96,9 @@ def serving_table(paths: list[str], requests, input_len, output_len, concurrency
 
 
 def launches_summary(path: str, forwards: int | None = None) -> str:
-    """Kernel launches per forward from an ncu ``--metrics gpu__time_duration.sum --csv`` launch list."""
+    """Kernel launches per forward from a launch list written by
+    ``ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file <path> <command>`` (one pass per
+    launch; ``--clock-control none`` keeps the profiler from locking the clocks of a shared GPU)."""
     lines = [ln for ln in Path(path).read_text().splitlines() if not ln.startswith("==")]
     names = Counter()
     total = Counter()

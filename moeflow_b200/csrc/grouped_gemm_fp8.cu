@@ -28,14 +28,14 @@
 
 #include "common.cuh"
 #include "moeflow_b200.h"
+#include "work_iter.cuh"
 
 namespace mf {
 
 constexpr int kF8BlockM = 128;
 constexpr int kF8TileA = 128 * 128;
-constexpr int kF8Threads = 256;
 constexpr int kF8Gather = 64;
-constexpr int kF8Tables = 3;  // scale tables: current unit, prefetched next unit, one in reserve
+constexpr int kF8Tables = 2;  // scale tables: the unit being promoted and the prefetched next one
 constexpr int kF8MaxKb = 32;  // K <= 4096 (one unit never spans more K blocks than this)
 
 template <bool kGateUp, int N_MAX>
@@ -44,9 +44,15 @@ struct F8Cfg {
   static constexpr int kStageA = kATiles * kF8TileA;
   static constexpr int kStageB = N_MAX * 128;
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kTableFloats = N_MAX * kF8MaxKb + 2 * kF8MaxKb;
+  // Promotion warps: one group of four warps (one per tensor-memory lane quarter) takes N_MAX / kGroups token
+  // columns.  128-column tiles use two groups, so that a thread keeps at most 2 x 64 running sums in
+  // registers and the per-K-block promotion has twice the issue slots.
+  static constexpr int kGroups = N_MAX > 64 ? 2 : 1;
+  static constexpr int kCols = N_MAX / kGroups;
+  static constexpr int kThreads = 128 + 128 * kGroups;
+  static constexpr int kTableFloats = N_MAX * kF8MaxKb + 2 * kF8MaxKb;  // x scales [kb][n], weight scales [2][kb]
   static constexpr int kTableBytes = kF8Tables * kTableFloats * 4;
-  static constexpr int kStages = (200 * 1024 - kTableBytes) / kStageBytes > 8 ? 8 : (200 * 1024 - kTableBytes) / kStageBytes;
+  static constexpr int kStages = (222 * 1024 - kTableBytes) / kStageBytes > 8 ? 8 : (222 * 1024 - kTableBytes) / kStageBytes;
   static constexpr int kTmpCols = kATiles * N_MAX;
   // One tensor-memory accumulator per K block in flight: the MMA -> promotion -> MMA round trip is about a
   // microsecond, so two stages cannot keep up with the weight stream; use all 512 columns (at most 8 stages).
@@ -67,10 +73,14 @@ struct F8Pipe {
 };
 
 template <bool kGateUp, int N_MAX>
-__global__ void __launch_bounds__(kF8Threads, 1)
-grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gemm_args a) {
+__global__ void __launch_bounds__(F8Cfg<kGateUp, N_MAX>::kThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_b,
+                        const mf_gemm_args a) {
   using Cfg = F8Cfg<kGateUp, N_MAX>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr int GROUPS = Cfg::kGroups;
+  constexpr int COLS = Cfg::kCols;
+  constexpr int PROMO_WARPS = 4 * GROUPS;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -82,24 +92,30 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tmp_full = bars + 2 * STAGES;
   uint64_t* tmp_empty = tmp_full + Cfg::kTmpStages;
-  uint64_t* tbl_bar = tmp_empty + Cfg::kTmpStages;  // [kF8Tables]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_bar + kF8Tables);
+  uint64_t* tbl_bar = tmp_empty + Cfg::kTmpStages;  // [kF8Tables] table filled
+  uint64_t* tbl_free = tbl_bar + kF8Tables;         // [kF8Tables] table no longer read
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_free + kF8Tables);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool b_tma = a.b_tmap != nullptr;  // token tiles by TMA (contiguous rows) instead of the 16-byte gather
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1 + kF8Gather);
+      mbar_init(&full_bar[s], b_tma ? 2 : 1 + kF8Gather);
       mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < Cfg::kTmpStages; ++s) {
       mbar_init(&tmp_full[s], 1);
-      mbar_init(&tmp_empty[s], 4);
+      mbar_init(&tmp_empty[s], PROMO_WARPS);
     }
-    for (int s = 0; s < kF8Tables; ++s) mbar_init(&tbl_bar[s], 4);
+    for (int s = 0; s < kF8Tables; ++s) {
+      mbar_init(&tbl_bar[s], PROMO_WARPS);
+      mbar_init(&tbl_free[s], PROMO_WARPS);
+    }
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
+    if (b_tma) tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -113,22 +129,38 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
   grid_dep_wait();
   grid_dep_launch();
 
-  const int n_tiles = a.plan[MF_PLAN_N_TILES];
-  int split = a.plan[a.split_word];
-  if (split < 1) split = 1;
-  const int kb_per = a.k_blocks / split;
-  const int total_units = n_tiles * a.m_blocks * split;
+  int n_tiles = a.plan[MF_PLAN_N_TILES];
+  const int cut = a.plan[a.split_word];  // 0 = stream-K, else the K split
+  int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
+  if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
+  const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kF8BlockM;
   const unsigned long long wait_ns = a.wait_ns;
+  WorkIter work;
+  work.init(a, N_MAX, n_tiles, cut, blockIdx.x, gridDim.x);
+  {
+    // the plan is checked against the buffers it indexes before anything is stored (same rule as the bf16 kernel)
+    bool bad = n_tiles < 0 || !(cut == 0 || cut == 1 || cut == 2 || cut == 4 || cut == 8) ||
+               (cut > 1 && a.k_blocks % cut != 0);
+    bad = bad || (a.max_tiles > 0 && n_tiles > a.max_tiles);
+    bad = bad || (a.n_counters > 0 && (long long)n_tiles * a.m_blocks * 4 * GROUPS > (long long)a.n_counters);
+    bad = bad || (a.partial_floats > 0 && work.slots_needed() * slot_floats > a.partial_floats);
+    if (bad) {
+      if (tid == 0) report_status(a.status, kBadArgument, 6, blockIdx.x, 0);
+      n_tiles = 0;
+      work.init(a, N_MAX, 0, 1, blockIdx.x, gridDim.x);
+    }
+  }
 
   if (warp == 0) {
     // ---------------------------------------------------------------- weight TMA producer
     F8Pipe st;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
-      const int row0 = a.tile_e[tt] * a.rows_per_expert + mb * kF8BlockM;
-      for (int j = 0; j < kb_per; ++j) {
-        const int kb = ks * kb_per + j;
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const int row0 = sg.e * a.rows_per_expert + sg.mb * kF8BlockM;
+      for (int j = 0; j < sg.nkb; ++j) {
+        const int kb = sg.kb0 + j;
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns));
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 0, blockIdx.x, 0);
@@ -152,13 +184,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
     // ---------------------------------------------------------------- UMMA issuer (one K block per tmp stage)
     F8Pipe st, tmp;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt];
-      uint32_t n_tile = (uint32_t)((n_rows + 15) & ~15);
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      uint32_t n_tile = (uint32_t)((sg.n_rows + 15) & ~15);
       if (n_tile < 16) n_tile = 16;
       const uint32_t idesc = umma_idesc(0, 0, kF8BlockM, n_tile);  // e4m3 x e4m3 -> fp32
-      for (int j = 0; j < kb_per; ++j) {
+      for (int j = 0; j < sg.nkb; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_empty[tmp.stage], tmp.phase ^ 1u, abort_flag, wait_ns));
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmAccTimeout, 1, blockIdx.x, 0);
@@ -189,15 +221,44 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
         tmp.advance(Cfg::kTmpStages);
       }
     }
+  } else if (warp < 4 && b_tma) {
+    // ---------------------------------------------------------------- token-operand producer (TMA)
+    if (warp == 2) {
+      F8Pipe st;
+      bool ok = true;
+      WorkIter it = work;
+      Seg sg;
+      while (ok && it.next(sg)) {
+        for (int j = 0; j < sg.nkb; ++j) {
+          const int kb = sg.kb0 + j;
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns));
+          if (!ok) {
+            if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 2, blockIdx.x, 0);
+            break;
+          }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageB);
+            tma_load_2d(sB + st.stage * Cfg::kStageB, &tmap_b, &full_bar[st.stage], kb * 128, sg.row_start);
+          }
+          __syncwarp();
+          st.advance(STAGES);
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 100000ull) __nanosleep(1000);
+      }
+    }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- token-operand producers (e4m3 rows)
     const int gt = tid - 64, r_in = gt >> 3, chunk = gt & 7;
     const uint32_t sw_off = (uint32_t)((chunk ^ r_in) << 4);
     F8Pipe st;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      const int ks = u % split, tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt];
+    WorkIter it = work;
+    Seg sg;
+    while (ok && it.next(sg)) {
+      const int n_rows = sg.n_rows, row_start = sg.row_start;
       int n_tile = (n_rows + 15) & ~15;
       if (n_tile < 16) n_tile = 16;
       const uint8_t* rp[N_MAX / 8];
@@ -210,8 +271,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
           rp[i] = static_cast<const uint8_t*>(a.b_base) + idx * a.b_pitch + chunk * 16;
         }
       }
-      for (int j = 0; j < kb_per; ++j) {
-        const int kb = ks * kb_per + j;
+      for (int j = 0; j < sg.nkb; ++j) {
+        const int kb = sg.kb0 + j;
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns));
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmEmptyTimeout, 2, blockIdx.x, 0);
@@ -233,83 +294,118 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
     asm volatile("cp.async.wait_all;" ::: "memory");
   } else {
     // ---------------------------------------------------------------- promotion + epilogue
-    const int wq = warp & 3, row = wq * 32 + lane;
+    const int pw = warp - 4;                 // 0 .. PROMO_WARPS-1
+    const int wq = pw & 3;                   // tensor-memory lane quarter
+    const int grp = pw >> 2;                 // column group
+    const int col0 = grp * COLS;
+    const int row = wq * 32 + lane;
     F8Pipe tmp;
     bool ok = true;
     const int row_blocks = a.rows_per_expert / kF8BlockM;
-    // Scale table of unit `uu` into buffer `buf`: x scales [n][j] and weight scales [t][j], j = kb - kb0.
-    // Every epilogue warp fills a quarter and arrives once on the buffer's barrier.
-    auto load_table = [&](int uu, int buf) {
-      const int ks_ = uu % split, mb_ = (uu / split) % a.m_blocks, tt_ = uu / (split * a.m_blocks);
-      const int n_rows_ = a.tile_n[tt_], row_start_ = a.tile_s[tt_], e_ = a.tile_e[tt_];
-      int n_tile_ = (n_rows_ + 15) & ~15;
+    // Scale table of one segment into buffer `buf`: x scales [j][n] and weight scales [t][j], j = kb - kb0.
+    // Every promotion warp fills its share (token columns n = pw, pw + PROMO_WARPS, ... in blocks of 32 lanes)
+    // and arrives once on the buffer's barrier.
+    auto load_table = [&](const Seg& s_, int buf) {
+      int n_tile_ = (s_.n_rows + 15) & ~15;
       if (n_tile_ < 16) n_tile_ = 16;
-      const int kb0_ = ks_ * kb_per;
       float* t = sTable + buf * Cfg::kTableFloats;
-      for (int n = wq; n < n_tile_; n += 4) {
-        const bool live = n < n_rows_;
-        long long idx = 0;
-        if (live) idx = a.b_index ? (long long)a.b_index[row_start_ + n] : (long long)(row_start_ + n);
-        for (int j = lane; j < kb_per; j += 32) t[n * kF8MaxKb + j] = live ? a.b_scale[idx * a.b_scale_pitch + kb0_ + j] : 0.f;
+      for (int n0 = pw * 32; n0 < n_tile_; n0 += PROMO_WARPS * 32) {
+        const int n = n0 + lane;
+        if (n < n_tile_) {
+          const bool live = n < s_.n_rows;
+          long long idx = 0;
+          if (live) idx = a.b_index ? (long long)a.b_index[s_.row_start + n] : (long long)(s_.row_start + n);
+          const float* src = a.b_scale + idx * a.b_scale_pitch + s_.kb0;
+          for (int j = 0; j < s_.nkb; ++j) t[j * N_MAX + n] = live ? __ldcg(src + j) : 0.f;
+        }
       }
-      if (wq < (kGateUp ? 2 : 1)) {
-        const int rb = (wq == 0 ? 0 : a.up_row_offset / kF8BlockM) + mb_;
-        const float* ws = a.w_scale + ((long long)e_ * row_blocks + rb) * a.k_blocks + kb0_;
-        for (int j = lane; j < kb_per; j += 32) t[N_MAX * kF8MaxKb + wq * kF8MaxKb + j] = ws[j];
+      if (pw < (kGateUp ? 2 : 1)) {
+        const int rb = (pw == 0 ? 0 : a.up_row_offset / kF8BlockM) + s_.mb;
+        const float* ws = a.w_scale + ((long long)s_.e * row_blocks + rb) * a.k_blocks + s_.kb0;
+        for (int j = lane; j < s_.nkb; j += 32) t[N_MAX * kF8MaxKb + pw * kF8MaxKb + j] = ws[j];
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&tbl_bar[buf]);
     };
-    if ((int)blockIdx.x < total_units) load_table(blockIdx.x, 0);
-    int it = 0;  // index of this CTA's unit
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
-      const int ks = u % split, mb = (u / split) % a.m_blocks, tt = u / (split * a.m_blocks);
-      const int n_rows = a.tile_n[tt], row_start = a.tile_s[tt];
+    WorkIter it = work;    // the segment being promoted
+    WorkIter ahead = work; // one segment ahead, for the table prefetch
+    Seg sg, nx;
+    bool have_next = ahead.next(nx);
+    if (have_next) load_table(nx, 0);
+    int n_it = 0;  // index of this CTA's segment
+    while (ok && it.next(sg)) {
+      const int mb = sg.mb, n_rows = sg.n_rows, row_start = sg.row_start;
       int n_tile = (n_rows + 15) & ~15;
       if (n_tile < 16) n_tile = 16;
-      const int buf = it % kF8Tables;
+      const int buf = n_it % kF8Tables;
       const float* tbl = sTable + buf * Cfg::kTableFloats;
       const float* tblW = tbl + N_MAX * kF8MaxKb;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_bar[buf], (uint32_t)(it / kF8Tables) & 1u, abort_flag, wait_ns));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_bar[buf], (uint32_t)(n_it / kF8Tables) & 1u, abort_flag, wait_ns));
       if (!ok) {
         if (lane == 0) report_status(a.status, kGemmAccTimeout, 4, blockIdx.x, 0);
         break;
       }
-      // Prefetch the next unit's table.  Its buffer was last read two units ago; having passed the wait
-      // above means all four warps filled table `it`, which they do inside unit `it - 1`, so no warp is
-      // still in unit `it - 2`.
-      if (u + (int)gridDim.x < total_units) load_table(u + gridDim.x, (it + 1) % kF8Tables);
-
-      float acc_g[N_MAX], acc_u[kGateUp ? N_MAX : 1];
-#pragma unroll
-      for (int i = 0; i < N_MAX; ++i) acc_g[i] = 0.f;
-      if (kGateUp) {
-#pragma unroll
-        for (int i = 0; i < N_MAX; ++i) acc_u[i] = 0.f;
+      // Prefetch the next segment's table into the other buffer, once every warp has stopped reading what
+      // that buffer held (the table of the previous segment).
+      have_next = ahead.next(nx);
+      if (have_next) {
+        const int nb = (n_it + 1) % kF8Tables;
+        if (n_it >= 1) {
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tbl_free[nb], (uint32_t)((n_it - 1) / kF8Tables) & 1u, abort_flag, wait_ns));
+          if (!ok) {
+            if (lane == 0) report_status(a.status, kGemmAccTimeout, 6, blockIdx.x, 0);
+            break;
+          }
+        }
+        load_table(nx, nb);
       }
 
-      for (int j = 0; j < kb_per; ++j) {
+      float acc_g[COLS], acc_u[kGateUp ? COLS : 1];
+#pragma unroll
+      for (int i = 0; i < COLS; ++i) acc_g[i] = 0.f;
+      if (kGateUp) {
+#pragma unroll
+        for (int i = 0; i < COLS; ++i) acc_u[i] = 0.f;
+      }
+
+      for (int j = 0; j < sg.nkb; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_full[tmp.stage], tmp.phase, abort_flag, wait_ns));
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
           break;
         }
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + tmp.stage * Cfg::kTmpCols;
+        const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + tmp.stage * Cfg::kTmpCols + col0;
         const float wsg = tblW[j];
         const float wsu = kGateUp ? tblW[kF8MaxKb + j] : 0.f;
+        const float4* xs4 = reinterpret_cast<const float4*>(tbl + j * N_MAX + col0);
 #pragma unroll
-        for (int c0 = 0; c0 < N_MAX; c0 += 16) {
-          if (c0 < n_tile) {
-            uint32_t g[16], up[16];
+        for (int c0 = 0; c0 < COLS; c0 += 16) {
+          if (col0 + c0 < n_tile) {
+            // gate and up one after the other (sixteen accumulator values live at a time, not thirty-two); the
+            // token scales are re-read from shared memory for the second pass instead of being kept
+            uint32_t g[16];
             tmem_ld_16(taddr + c0, g);
-            if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float xs = tbl[(c0 + i) * kF8MaxKb + j];
-              acc_g[c0 + i] = fmaf(__uint_as_float(g[i]), wsg * xs, acc_g[c0 + i]);
-              if (kGateUp) acc_u[c0 + i] = fmaf(__uint_as_float(up[i]), wsu * xs, acc_u[c0 + i]);
+            for (int q = 0; q < 4; ++q) {
+              const float4 xs = xs4[c0 / 4 + q];
+              acc_g[c0 + 4 * q] = fmaf(__uint_as_float(g[4 * q]), wsg * xs.x, acc_g[c0 + 4 * q]);
+              acc_g[c0 + 4 * q + 1] = fmaf(__uint_as_float(g[4 * q + 1]), wsg * xs.y, acc_g[c0 + 4 * q + 1]);
+              acc_g[c0 + 4 * q + 2] = fmaf(__uint_as_float(g[4 * q + 2]), wsg * xs.z, acc_g[c0 + 4 * q + 2]);
+              acc_g[c0 + 4 * q + 3] = fmaf(__uint_as_float(g[4 * q + 3]), wsg * xs.w, acc_g[c0 + 4 * q + 3]);
+            }
+            if (kGateUp) {
+              tmem_ld_16(taddr + N_MAX + c0, g);
+              tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 xs = xs4[c0 / 4 + q];
+                acc_u[c0 + 4 * q] = fmaf(__uint_as_float(g[4 * q]), wsu * xs.x, acc_u[c0 + 4 * q]);
+                acc_u[c0 + 4 * q + 1] = fmaf(__uint_as_float(g[4 * q + 1]), wsu * xs.y, acc_u[c0 + 4 * q + 1]);
+                acc_u[c0 + 4 * q + 2] = fmaf(__uint_as_float(g[4 * q + 2]), wsu * xs.z, acc_u[c0 + 4 * q + 2]);
+                acc_u[c0 + 4 * q + 3] = fmaf(__uint_as_float(g[4 * q + 3]), wsu * xs.w, acc_u[c0 + 4 * q + 3]);
+              }
             }
           }
         }
@@ -319,16 +415,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
         tmp.advance(Cfg::kTmpStages);
       }
       if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tbl_free[buf]);  // this warp is done with the segment's table
 
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
       const long long out_col = (long long)mb * kF8BlockM + row;
-      if (split == 1) {
+      if (sg.nseg == 1) {
 #pragma unroll
-        for (int n = 0; n < N_MAX; ++n) {
+        for (int c = 0; c < COLS; ++c) {
+          const int n = col0 + c;
           if (n < n_rows) {
-            float v = acc_g[n];
+            float v = acc_g[c];
             if (kGateUp) {
-              float w = acc_u[n];
+              float w = acc_u[c];
               if (a.round_h) {
                 v = bf16_round(v);
                 w = bf16_round(w);
@@ -341,48 +440,69 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const mf_gem
           }
         }
       } else {
-        const int tile_mb = tt * a.m_blocks + mb;
-        int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
-        if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
-        const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kF8BlockM;
-        float* mine = a.partial + ((long long)tile_mb * split + ks) * slot_floats;
+        float* mine = a.partial + (long long)it.slot_of(sg, sg.seg) * slot_floats;
 #pragma unroll
-        for (int n = 0; n < N_MAX; ++n) {
+        for (int c = 0; c < COLS; ++c) {
+          const int n = col0 + c;
           if (n < n_rows) {
-            __stcg(&mine[(long long)n * kF8BlockM + row], acc_g[n]);
-            if (kGateUp) __stcg(&mine[(long long)(slot_cols + n) * kF8BlockM + row], acc_u[n]);
+            __stcg(&mine[(long long)n * kF8BlockM + row], acc_g[c]);
+            if (kGateUp) __stcg(&mine[(long long)(slot_cols + n) * kF8BlockM + row], acc_u[c]);
           }
         }
         __threadfence();
         __syncwarp();
+        int* counter = a.counters + ((long long)sg.unit * 4 + wq) * GROUPS + grp;
         int old = 0;
-        if (lane == 0) old = atomicAdd(&a.counters[tile_mb * 4 + wq], 1);
+        if (lane == 0) old = atomicAdd(counter, 1);
         old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == split - 1) {
+        if (old == sg.nseg - 1) {
           __threadfence();
-          const float* base = a.partial + (long long)tile_mb * split * slot_floats;
-          for (int n = 0; n < n_rows; ++n) {
-            float v = 0.f, w = 0.f;
-            for (int s = 0; s < split; ++s) {
-              const float* p = base + s * slot_floats;
-              v += __ldcg(&p[(long long)n * kF8BlockM + row]);
-              if (kGateUp) w += __ldcg(&p[(long long)(slot_cols + n) * kF8BlockM + row]);
-            }
-            if (kGateUp) {
-              if (a.round_h) {
-                v = bf16_round(v);
-                w = bf16_round(w);
+          constexpr int kFix = 8;
+          const int n_end = n_rows < col0 + COLS ? n_rows : col0 + COLS;
+          for (int n0 = col0; n0 < n_end; n0 += kFix) {
+            float v[kFix], w[kFix];
+#pragma unroll
+            for (int jx = 0; jx < kFix; ++jx) v[jx] = w[jx] = 0.f;
+            for (int s_ = 0; s_ < sg.nseg; ++s_) {
+              const float* p = a.partial + (long long)it.slot_of(sg, s_) * slot_floats;
+              float pv[kFix], pw_[kFix];
+#pragma unroll
+              for (int jx = 0; jx < kFix; ++jx) {
+                const int n = n0 + jx;
+                pv[jx] = n < n_end ? __ldcg(&p[(long long)n * kF8BlockM + row]) : 0.f;
+                pw_[jx] = (kGateUp && n < n_end) ? __ldcg(&p[(long long)(slot_cols + n) * kF8BlockM + row]) : 0.f;
               }
-              v = swiglu_clamped(v, w, a.limit);
-            } else if (a.row_scale) {
-              v *= a.row_scale[row_start + n];
+#pragma unroll
+              for (int jx = 0; jx < kFix; ++jx) {
+                v[jx] += pv[jx];
+                w[jx] += pw_[jx];
+              }
             }
-            out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+#pragma unroll
+            for (int jx = 0; jx < kFix; ++jx) {
+              const int n = n0 + jx;
+              if (n < n_end) {
+                float r = v[jx];
+                if (kGateUp) {
+                  float u = w[jx];
+                  if (a.round_h) {
+                    r = bf16_round(r);
+                    u = bf16_round(u);
+                  }
+                  r = swiglu_clamped(r, u, a.limit);
+                } else if (a.row_scale) {
+                  r *= a.row_scale[row_start + n];
+                }
+                out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(r);
+              }
+            }
           }
-          if (lane == 0) a.counters[tile_mb * 4 + wq] = 0;
+          if (lane == 0) *counter = 0;
         }
       }
+      ++n_it;
     }
+    if (it.bad_tile && pw == 0 && lane == 0) report_status(a.status, kBadArgument, 7, blockIdx.x, 0);
   }
 
   __syncwarp();
@@ -460,14 +580,16 @@ static int launch_f8(const void* tmap, const mf_gemm_args* args, int grid, cudaS
     if (e != cudaSuccess) return (int)e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  CUtensorMap tm;
+  CUtensorMap tm, tb;
   memcpy(&tm, tmap, sizeof(tm));
-  return (int)launch_kernel(kern, dim3(grid), dim3(kF8Threads), Cfg::kSmemBytes, stream, true, tm, *args);
+  memcpy(&tb, args->b_tmap ? args->b_tmap : tmap, sizeof(tb));
+  return (int)launch_kernel(kern, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream, true, tm, tb, *args);
 }
 
 static int check_f8(const mf_gemm_args* a, int n_max, int grid) {
   if (!a || grid < 1) return -1;
-  if (n_max != 32 && n_max != 64) return -2;
+  if (n_max != 32 && n_max != 64 && n_max != 128) return -2;
+  if (a->b_tmap != nullptr && a->b_index != nullptr) return -6;  // TMA token tiles need contiguous rows
   if (a->m_blocks < 1 || a->k_blocks < 1 || a->k_blocks > kF8MaxKb) return -3;
   if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
   if (!a->w_scale || !a->b_scale) return -5;
@@ -483,7 +605,8 @@ int mf_gemm_gate_up_fp8(const void* tmap, const mf_gemm_args* args, int n_max, i
   if (c) return c;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n_max == 32) return mf::launch_f8<true, 32>(tmap, args, grid, s);
-  return mf::launch_f8<true, 64>(tmap, args, grid, s);
+  if (n_max == 64) return mf::launch_f8<true, 64>(tmap, args, grid, s);
+  return mf::launch_f8<true, 128>(tmap, args, grid, s);
 }
 
 int mf_gemm_down_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
@@ -491,7 +614,8 @@ int mf_gemm_down_fp8(const void* tmap, const mf_gemm_args* args, int n_max, int 
   if (c) return c;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n_max == 32) return mf::launch_f8<false, 32>(tmap, args, grid, s);
-  return mf::launch_f8<false, 64>(tmap, args, grid, s);
+  if (n_max == 64) return mf::launch_f8<false, 64>(tmap, args, grid, s);
+  return mf::launch_f8<false, 128>(tmap, args, grid, s);
 }
 
 int mf_quant_rows_1x128(const void* x, long long x_pitch, const int* row_index, int rows, int hidden, void* q,

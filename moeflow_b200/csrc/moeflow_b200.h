@@ -59,7 +59,7 @@ typedef struct {
   // return flags.  Needs the plan word MF_PLAN_VALID_ROWS and row_hits from mf_expert_meta.
   const unsigned long long* ret_peer;   // [R] base addresses of every rank's ret_recv [R, C, H]
   const unsigned long long* ret_flag;   // [R] base addresses of every rank's return flags [R]
-  const unsigned* ret_epoch;
+  unsigned* ret_epoch;       // this rank's count of return pushes (incremented by the warp that publishes)
   unsigned* ret_done;        // completion counter, zero between launches
   int* row_cnt;              // [rows * m_blocks * 4] arrival counters, zero between launches (self-cleaning)
   const int* row_hits;       // [rows] valid slots of each received row on this rank
@@ -215,6 +215,7 @@ typedef struct {
   unsigned* done_counter;
   int R, C, H, K, rank;
   int valid_word;            // index of the valid flag among a row's int32 metadata words (2 * top_k)
+  unsigned* push_epoch;      // local count of return pushes; the last CTA adds one (the combine's expectation)
 } mf_reduce_push_args;
 int mf_owner_reduce_push(const mf_reduce_push_args* args, mf_stream_t stream);
 
@@ -222,8 +223,8 @@ typedef struct {
   const void* ret;           // local ret_recv [R, C, H] bf16
   const unsigned char* hit;  // [C, R]
   void* out;                 // [C, H] bf16
-  const unsigned* flags;     // [R] return flags (local), may be NULL
-  const unsigned* epoch;
+  const unsigned* flags;     // [R] return flags (local), may be NULL: counting flags, C arrivals per return push
+  const unsigned* epoch;     // this rank's count of return pushes (every rank runs the same launch sequence)
   int R, C, H, rank;
   int ring;                  // 1: order (rank+1 .. rank+R) % R with bf16 rounding after every add
   unsigned long long* status;

@@ -85,6 +85,14 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   if (tid == 0) {
     __threadfence_system();
     red_add_relaxed_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[s]) + a.rank, 1u);
+    // Off the critical path: the last CTA counts this push locally.  The combine of this rank expects
+    // push_epoch * C arrivals from every owner (all ranks run the same sequence of launches, so their push
+    // counts agree), which stays right when some forwards are cut short before the return path.
+    const unsigned done = atomicAdd(a.done_counter, 1u);
+    if (done == gridDim.x - 1) {
+      *a.done_counter = 0u;
+      if (a.push_epoch != nullptr) *a.push_epoch += 1u;
+    }
   }
 }
 

@@ -435,6 +435,7 @@ class FixedEPLayer:
         self._route_ids = torch.zeros(Cc, K, **i32)
         self._epoch = torch.zeros(1, **i32)
         self._done = torch.zeros(4, **i32)
+        self._push_epoch = torch.zeros(1, **i32)  # return pushes so far (the combine expects this many x C arrivals)
         self.status = torch.zeros(1, dtype=torch.int64, device=dev)
         self.offsets = torch.zeros(L + 1, **i32)
         self.entry_row = torch.zeros(N, **i32)
@@ -448,8 +449,10 @@ class FixedEPLayer:
         self.act = torch.zeros(max(N, self.block_m), I, dtype=torch.bfloat16, device=dev)  # >= one TMA box of rows
         self.y = torch.zeros(N, H, dtype=torch.bfloat16, device=dev)
         mb1, mb2 = I // 128, H // 128
-        self._counters1 = torch.zeros(self.max_tiles * mb1 * 4, **i32)
-        self._counters2 = torch.zeros(self.max_tiles * mb2 * 4, **i32)
+        # arrival counters of cut units: one per (unit, 32-row quarter) and, in the fp8 kernels with 128-column
+        # tiles, per column group (two)
+        self._counters1 = torch.zeros(self.max_tiles * mb1 * 8, **i32)
+        self._counters2 = torch.zeros(self.max_tiles * mb2 * 8, **i32)
         # split-K scratch: a byte budget; the metadata kernel sizes the partial slots for the widest token tile
         partial_floats = int(self.gemm_kwargs.get("split_scratch_mb", 64)) * (1 << 20) // 4
         self.max_split_slots = partial_floats // (2 * self.block_m * 128)
@@ -477,7 +480,7 @@ class FixedEPLayer:
             n_counters2=self._counters2.numel(), block_m=self.block_m, max_tiles=self.max_tiles, m_blocks1=mb1,
             k_blocks1=H // 64, m_blocks2=mb2, k_blocks2=I // 64, n_sms=self.n_sms,
             max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
-            partial_floats=partial_floats, stream_k=int(self.gemm_kwargs.get("stream_k", 1)),
+            partial_floats=partial_floats, stream_k=int(self.gemm_kwargs.get("stream_k", 0)),
         )
         # Metadata: one CTA for decode sizes; for prefill sizes (many received rows) the counting sort is
         # split over several CTAs in two chained launches.  Same result either way.
@@ -542,7 +545,7 @@ class FixedEPLayer:
             self._row_cnt = torch.zeros(R * Cc * mb2 * 4, **i32)
             g2 = self._a_gemm2
             g2.ret_peer, g2.ret_flag = self._peer_ret.data_ptr(), self._peer_rflag.data_ptr()
-            g2.ret_epoch, g2.ret_done = self._epoch.data_ptr(), self._done[3:].data_ptr()
+            g2.ret_epoch, g2.ret_done = self._push_epoch.data_ptr(), self._done[3:].data_ptr()
             g2.row_cnt, g2.row_hits = self._row_cnt.data_ptr(), self.row_hits.data_ptr()
             g2.entry_row, g2.inv = self.entry_row.data_ptr(), self.inv.data_ptr()
             g2.ret_rank, g2.ret_R, g2.ret_C, g2.ret_K = self.rank, R, Cc, K
@@ -550,17 +553,19 @@ class FixedEPLayer:
             y=self.y.data_ptr(), inv=self.inv.data_ptr(), recv=self._recv_store.data_ptr(), pitch=self.pitch * 2,
             peer_ret=self._peer_ret.data_ptr(), peer_flag=self._peer_rflag.data_ptr(), epoch=self._epoch.data_ptr(),
             done_counter=self._done[1:].data_ptr(), R=R, C=Cc, H=H, K=K, rank=self.rank, valid_word=2 * K,
+            push_epoch=self._push_epoch.data_ptr(),
         )
         self._row_ids = torch.arange(R * Cc, **i32)
         self._a_push = S.ReducePushArgs(
             y=None, inv=self._row_ids.data_ptr(), recv=self._recv_store.data_ptr(), pitch=self.pitch * 2,
             peer_ret=self._peer_ret.data_ptr(), peer_flag=self._peer_rflag.data_ptr(), epoch=self._epoch.data_ptr(),
             done_counter=self._done[2:].data_ptr(), R=R, C=Cc, H=H, K=1, rank=self.rank, valid_word=2 * K,
+            push_epoch=self._push_epoch.data_ptr(),
         )
         self._scratch_out = None
         self._a_combine = S.CombineArgs(
             ret=self.ret_recv.data_ptr(), hit=self.hit.data_ptr(), out=self.out.data_ptr(),
-            flags=self._ret_flags.data_ptr(), epoch=self._epoch.data_ptr(), R=R, C=Cc, H=H, rank=self.rank,
+            flags=self._ret_flags.data_ptr(), epoch=self._push_epoch.data_ptr(), R=R, C=Cc, H=H, rank=self.rank,
             ring=int(self.combine_mode == "bf16_ring"), status=self.status.data_ptr(), wait_ns=self.wait_ns,
         )
         self._tmap13 = self._tmap2 = None
@@ -603,8 +608,8 @@ class FixedEPLayer:
             raise ValueError("e4m3 weights expected")
         if tuple(w13_s.shape) != (L, 2 * I // 128, H // 128) or tuple(w2_s.shape) != (L, H // 128, I // 128):
             raise ValueError("scales must be one fp32 per 128x128 block")
-        if H > 4096 or I > 4096 or self.block_m > 64:
-            raise ValueError("fp8 path supports K <= 4096 and block_m <= 64 (build the layer with gemm_kwargs={'block_m': 64})")
+        if H > 4096 or I > 4096:
+            raise ValueError("fp8 path supports K <= 4096")
         dev = self.device
         f = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
              "s2": w2_s.to(torch.float32).contiguous()}
@@ -613,8 +618,8 @@ class FixedEPLayer:
         rows = self.world * self.C
         f["xq"] = torch.zeros(rows, H, dtype=torch.uint8, device=dev)
         f["xs"] = torch.zeros(rows, H // 128, dtype=torch.float32, device=dev)
-        f["aq"] = torch.zeros(N, I, dtype=torch.uint8, device=dev)
-        f["as"] = torch.zeros(N, I // 128, dtype=torch.float32, device=dev)
+        f["aq"] = torch.zeros(max(N, self.block_m), I, dtype=torch.uint8, device=dev)  # >= one TMA box of rows
+        f["as"] = torch.zeros(max(N, self.block_m), I // 128, dtype=torch.float32, device=dev)
         g1, g2 = self._a_gemm1, self._a_gemm2
         common = dict(tile_e=g1.tile_e, tile_s=g1.tile_s, tile_n=g1.tile_n, plan=g1.plan, partial=g1.partial,
                       max_split_slots=g1.max_split_slots, limit=g1.limit, round_h=0, status=g1.status, wait_ns=g1.wait_ns,
@@ -627,6 +632,11 @@ class FixedEPLayer:
                                 m_blocks=H // 128, k_blocks=I // 128, rows_per_expert=H, up_row_offset=0,
                                 out=self.y.data_ptr(), out_pitch=H, row_scale=self.entry_w.data_ptr(), counters=g2.counters,
                                 n_counters=g2.n_counters, w_scale=f["s2"].data_ptr(), b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128, **common)
+        if bool(self.gemm_kwargs.get("b_tma", True)):
+            from .ops.kernels import make_tile_tmap
+
+            f["tm_aq"] = make_tile_tmap(f["aq"], self.block_m)  # the down GEMM reads its e4m3 token tiles by TMA
+            f["a2"].b_tmap = C.addressof(f["tm_aq"])
         self._fp8 = f
         self._tmap13, self._tmap2 = f["tm13"], f["tm2"]
 

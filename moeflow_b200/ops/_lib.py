@@ -168,6 +168,7 @@ class ReducePushArgs(C.Structure):
         ("K", C.c_int),
         ("rank", C.c_int),
         ("valid_word", C.c_int),
+        ("push_epoch", C.c_void_p),
     ]
 
 

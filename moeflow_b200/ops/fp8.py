@@ -17,7 +17,7 @@ import torch
 
 from . import _lib
 from .grouped_gemm import TilePlan, _scratch
-from .kernels import make_weight_tmap, sm_count
+from .kernels import make_tile_tmap, make_weight_tmap, sm_count
 
 E4M3_MAX = 448.0
 
@@ -54,7 +54,8 @@ def quant_rows_1x128(x: torch.Tensor, row_index: torch.Tensor | None = None, row
     return q, s
 
 
-def _gemm_fp8(gate_up: bool, xq, xs, wq, ws, tp: TilePlan, out, row_index, row_scale, limit, split, status, wait_ns, grid):
+def _gemm_fp8(gate_up: bool, xq, xs, wq, ws, tp: TilePlan, out, row_index, row_scale, limit, split, status, wait_ns, grid,
+              b_tma: bool = False):
     n_exp, rows, k = wq.shape
     if xq.dtype != torch.float8_e4m3fn or wq.dtype != torch.float8_e4m3fn:
         raise ValueError("e4m3 operands expected")
@@ -80,7 +81,19 @@ def _gemm_fp8(gate_up: bool, xq, xs, wq, ws, tp: TilePlan, out, row_index, row_s
         out=out.data_ptr(), out_pitch=out.shape[1], row_scale=_lib.ptr(row_scale), partial=partial.data_ptr(),
         counters=counters.data_ptr(), max_split_slots=slots, limit=float(limit) if limit is not None else 0.0, round_h=0,
         status=status.data_ptr(), wait_ns=wait_ns, w_scale=ws.data_ptr(), b_scale=xs.data_ptr(), b_scale_pitch=xs.stride(0),
+        partial_floats=partial.numel(), n_counters=counters.numel(), max_tiles=tp.tile_e.numel(),
     )
+    tmap_b = None
+    if b_tma:
+        if row_index is not None or not xq.is_contiguous():
+            raise ValueError("token tiles by TMA need contiguous rows and no row index")
+        xq8 = xq.view(torch.uint8)
+        if xq8.shape[0] < tp.block_m:  # the tensor map needs at least one box of rows
+            xq8 = torch.cat([xq8, xq8.new_zeros(tp.block_m - xq8.shape[0], k)])
+            args.b_base = xq8.data_ptr()
+        tmap_b = make_tile_tmap(xq8, tp.block_m)
+        args.b_tmap = C.addressof(tmap_b)
+        xq = xq8
     fn = _lib.lib().mf_gemm_gate_up_fp8 if gate_up else _lib.lib().mf_gemm_down_fp8
     _lib.check(fn(tmap, C.byref(args), tp.block_m, grid, _lib.stream_ptr()), "fp8 gemm")
     out._keep = (wq, ws, partial, counters, status, xq, xs, row_index, row_scale)
@@ -95,8 +108,11 @@ def gate_up_swiglu_fp8(xq, xs, w13_q, w13_s, tp: TilePlan, row_index=None, limit
     return _gemm_fp8(True, xq, xs, w13_q, w13_s, tp, act, row_index, None, limit, split, status, wait_ns, grid)[: tp.n_entries]
 
 
-def down_proj_fp8(aq, a_s, w2_q, w2_s, tp: TilePlan, row_scale=None, split=1, status=None, wait_ns=2_000_000_000, grid=None):
-    """``y [N, H]`` bf16 = ``row_scale * (dequant(aq) . dequant(w2)^T)``."""
+def down_proj_fp8(aq, a_s, w2_q, w2_s, tp: TilePlan, row_scale=None, split=1, status=None, wait_ns=2_000_000_000, grid=None,
+                  b_tma: bool = True):
+    """``y [N, H]`` bf16 = ``row_scale * (dequant(aq) . dequant(w2)^T)``; ``b_tma``: token tiles by TMA or by the
+    16-byte gather."""
     hidden = w2_q.shape[1]
     y = torch.zeros(max(tp.n_entries, 1), hidden, dtype=torch.bfloat16, device=aq.device)
-    return _gemm_fp8(False, aq, a_s, w2_q, w2_s, tp, y, None, row_scale, None, split, status, wait_ns, grid)[: tp.n_entries]
+    return _gemm_fp8(False, aq, a_s, w2_q, w2_s, tp, y, None, row_scale, None, split, status, wait_ns, grid,
+                     b_tma=b_tma)[: tp.n_entries]

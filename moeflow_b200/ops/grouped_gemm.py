@@ -60,7 +60,7 @@ def _scratch(tp: TilePlan, m_blocks: int, split: int, device, grid: int):
     stream-K) two tiles per CTA."""
     slots = max(1, 2 * grid if split == 0 else tp.n_tiles * m_blocks * split)
     partial = torch.empty(slots * 2 * tp.block_m * 128 if split != 1 else 1, dtype=torch.float32, device=device)
-    counters = torch.zeros(max(1, tp.n_tiles) * m_blocks * 4, dtype=torch.int32, device=device)
+    counters = torch.zeros(max(1, tp.n_tiles) * m_blocks * 8, dtype=torch.int32, device=device)  # x2: fp8 column groups
     return partial, counters, slots
 
 

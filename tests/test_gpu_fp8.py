@@ -81,13 +81,16 @@ def _fp8_problem(counts, hidden, inter, seed):
 
 
 @pytest.mark.parametrize("counts,hidden,inter,block_m", [([1], 256, 128, 64), ([3, 0, 17, 5], 512, 256, 64),
-                                                          ([70, 2, 33], 1024, 384, 64), ([9, 30], 512, 256, 32)])
-@pytest.mark.parametrize("split", [1, 2])
+                                                          ([70, 2, 33], 1024, 384, 64), ([9, 30], 512, 256, 32),
+                                                          ([128], 256, 128, 128), ([300, 5, 129], 512, 256, 128),
+                                                          ([100, 20, 64], 1024, 384, 128)])
+@pytest.mark.parametrize("split", [0, 1, 2])
 def test_fp8_gemms_match_dequantised_definition(counts, hidden, inter, block_m, split):
+    """K cuts 1 and 2, and 0 = stream-K; token tiles of 32, 64 and 128 rows (128: two promotion warp groups)."""
     from moeflow_b200.ops.fp8 import dequant_rows, down_proj_fp8, gate_up_swiglu_fp8, quant_rows_1x128
     from moeflow_b200.ops.grouped_gemm import plan_from_offsets
 
-    if (inter // 128) % split:
+    if split and (inter // 128) % split:
         pytest.skip("split does not divide the K blocks of the down GEMM")
     q13, s13, q2, s2, x, idx, offsets, scale = _fp8_problem(counts, hidden, inter, seed=hidden + len(counts))
     n = offsets[-1]
@@ -107,8 +110,10 @@ def test_fp8_gemms_match_dequantised_definition(counts, hidden, inter, block_m, 
 
     aq, a_s = quant_rows_1x128(act.contiguous())
     y = down_proj_fp8(aq, a_s, q2, s2, tp, row_scale=scale, split=split, status=status, wait_ns=50_000_000)
+    y_gather = down_proj_fp8(aq, a_s, q2, s2, tp, row_scale=scale, split=split, status=status, wait_ns=50_000_000, b_tma=False)
     torch.cuda.synchronize()
     _ok(status)
+    assert torch.equal(y.view(torch.int16), y_gather.view(torch.int16)), "token tiles by TMA and by gather differ"
     a_dq = dequant_rows(aq, a_s)
     ref_y = torch.zeros(n, hidden, device="cuda")
     for e, (lo, hi) in enumerate(zip(offsets[:-1], offsets[1:])):
