@@ -52,6 +52,7 @@ def main() -> None:
     ap.add_argument("--permute-rows", action="store_true",
                     help="copy received rows into expert-major order so the gate/up GEMM reads token tiles by TMA")
     ap.add_argument("--fuse-return", type=int, default=None, help="1/0: owner reduce + return push inside the down GEMM or as its own kernel")
+    ap.add_argument("--tile-handover", type=int, default=None, help="1/0: the down GEMM starts a tile when its activations are final, or after the whole gate/up grid")
     ap.add_argument("--stream-k", type=int, default=None, help="1/0: allow the stream-K cut of the GEMMs' K steps or K splits only")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights (quantised from the bf16 ones)")
     ap.add_argument("--out", default=None)
@@ -89,6 +90,7 @@ def main() -> None:
                                           **({"meta_ctas": args.meta_ctas} if args.meta_ctas else {}),
                                           **({"permute_rows": True} if args.permute_rows else {}),
                                           **({"stream_k": args.stream_k} if args.stream_k is not None else {}),
+                                          **({"tile_handover": bool(args.tile_handover)} if args.tile_handover is not None else {}),
                                           **({"fuse_return": bool(args.fuse_return)} if args.fuse_return is not None else {})})
         if args.fp8:
             layer.set_weights_fp8(*fp8_pack)

@@ -37,13 +37,15 @@ def main() -> None:
     ap.add_argument("--intermediate", type=int, default=1536)
     ap.add_argument("--chunk", type=int, default=64, help="decode steps per timing sample")
     ap.add_argument("--no-attention", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 routed experts (128x128 weight blocks, 1x128 activation groups)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     info = init_dist()
     cfg = dataclasses.replace(GLM53_FLASH_I1536, moe_intermediate_size=args.intermediate)
     batch = max(1, (args.concurrency + info.world - 1) // info.world)
     acfg = AttentionConfig(max_seq=args.input_len + args.output_len + 8)
-    model = DecodeModel(cfg, info.rank, info.world, batch, args.layers, info.device, acfg, attention=not args.no_attention)
+    model = DecodeModel(cfg, info.rank, info.world, batch, args.layers, info.device, acfg, attention=not args.no_attention,
+                        fp8=args.fp8)
     model.prefill_standin(args.input_len)
     model.x.copy_(torch.randn(batch, cfg.hidden_size, device=info.device).bfloat16())
     model.capture()

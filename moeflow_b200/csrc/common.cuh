@@ -85,6 +85,15 @@ __device__ __forceinline__ void publish_flags(const unsigned long long* peer_fla
   __threadfence_system();
   for (int d = 0; d < n_peers; ++d) st_relaxed_sys_u32(reinterpret_cast<unsigned*>(peer_flag[d]) + rank, value);
 }
+// Fence between a CTA's row stores and its arrival: system scope when the rows went to peers' memory, device
+// scope when the only rank is this GPU (the system-scope fence costs microseconds even without a peer).
+__device__ __forceinline__ void fence_before_arrival(int n_ranks) {
+  if (n_ranks > 1)
+    __threadfence_system();
+  else
+    __threadfence();
+}
+
 // Counting flags: every CTA that has finished its share of a transfer adds one to word [rank] of the
 // destination's flag array, after a system-scope fence that orders the CTA's peer stores before it.  The
 // waiter knows how many arrivals a forward brings (epoch * arrivals per forward), so no CTA has to be the
@@ -96,6 +105,28 @@ __device__ __forceinline__ unsigned ld_relaxed_sys_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Orders later async-proxy accesses (TMA) of this thread after its earlier generic-proxy accesses: needed when
+// data written with ordinary stores by another CTA is fetched by TMA after a flag handshake.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Bounded wait for a device-scope counter to reach `want`.
+__device__ __forceinline__ bool wait_count_ge_gpu(const int* counter, int want, unsigned long long limit_ns) {
+  if (ld_acquire_gpu_s32(counter) >= want) return true;
+  const unsigned long long t0 = global_timer_ns();
+  unsigned spins = 0;
+  while (true) {
+    if (ld_acquire_gpu_s32(counter) >= want) return true;
+    if ((++spins & 63u) == 0u) {
+      if (global_timer_ns() - t0 > limit_ns) return false;
+    }
+    __nanosleep(32);
+  }
 }
 
 // Spin until *flag >= want (wrap-safe signed difference) or until `limit_ns` has passed.
@@ -245,6 +276,19 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t (&r)[16]) {
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
 }

@@ -33,6 +33,8 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
 
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
+  unsigned long long* trace = (a.trace != nullptr && blockIdx.x == 0 && tid == 0) ? a.trace : nullptr;
+  if (trace) trace[0] = global_timer_ns();
   grid_dep_launch();  // the metadata kernel may get resident now; it waits for this grid to complete
   const unsigned epoch_next = *a.epoch + 1u;
   const bool has_token = t < a.T;
@@ -75,6 +77,7 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
     }
   }
   __syncthreads();
+  if (trace) trace[1] = global_timer_ns();  // routed, hidden row loaded
 
   // Which destinations does this token hit?  One thread per destination, once; the copy loop below then
   // needs no barrier, so the stores to all peers are in flight together.
@@ -111,8 +114,10 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
   // Publish: the barrier orders every thread's stores before the system fence of warp 0's lanes (cumulative);
   // then one arrival per destination, issued by different lanes so that they travel together.
   __syncthreads();
+  if (trace) trace[2] = global_timer_ns();  // rows stored
   if (tid < 32) {
-    __threadfence_system();
+    fence_before_arrival(a.R);
+    if (trace) trace[3] = global_timer_ns();  // fenced
     for (int d = tid; d < a.R; d += 32) red_add_relaxed_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[d]) + a.rank, 1u);
     if (tid == 0) {
       // the local epoch (read by this rank's later kernels after this grid has completed)
@@ -120,8 +125,10 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
       if (done == gridDim.x - 1) {
         *a.done_counter = 0u;
         *a.epoch = epoch_next;
+        if (a.trace) a.trace[5] = global_timer_ns();  // last CTA done
       }
     }
+    if (trace) trace[4] = global_timer_ns();  // arrivals sent
   }
 }
 

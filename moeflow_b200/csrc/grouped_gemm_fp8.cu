@@ -45,9 +45,9 @@ struct F8Cfg {
   static constexpr int kStageB = N_MAX * 128;
   static constexpr int kStageBytes = kStageA + kStageB;
   // Promotion warps: one group of four warps (one per tensor-memory lane quarter) takes N_MAX / kGroups token
-  // columns.  128-column tiles use two groups, so that a thread keeps at most 2 x 64 running sums in
-  // registers and the per-K-block promotion has twice the issue slots.
-  static constexpr int kGroups = N_MAX > 64 ? 2 : 1;
+  // columns: 32 columns per group for tiles of up to 64 rows (a K block's promotion is then one tensor-memory
+  // round trip per warp), 64 for 128-row tiles (a thread keeps at most 2 x 64 running sums in registers).
+  static constexpr int kGroups = N_MAX > 32 ? 2 : 1;
   static constexpr int kCols = N_MAX / kGroups;
   static constexpr int kThreads = 128 + 128 * kGroups;
   static constexpr int kTableFloats = N_MAX * kF8MaxKb + 2 * kF8MaxKb;  // x scales [kb][n], weight scales [2][kb]
@@ -379,16 +379,18 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const float wsg = tblW[j];
         const float wsu = kGateUp ? tblW[kF8MaxKb + j] : 0.f;
         const float4* xs4 = reinterpret_cast<const float4*>(tbl + j * N_MAX + col0);
+        // Thirty-two token columns per tensor-memory round trip (the load latency, not the arithmetic, bounds a
+        // K block's promotion); with 32-column groups the gate and the up values travel together.
+        constexpr bool kBoth = kGateUp && COLS == 32;
 #pragma unroll
-        for (int c0 = 0; c0 < COLS; c0 += 16) {
+        for (int c0 = 0; c0 < COLS; c0 += 32) {
           if (col0 + c0 < n_tile) {
-            // gate and up one after the other (sixteen accumulator values live at a time, not thirty-two); the
-            // token scales are re-read from shared memory for the second pass instead of being kept
-            uint32_t g[16];
-            tmem_ld_16(taddr + c0, g);
+            uint32_t g[32], u2[kBoth ? 32 : 1];
+            tmem_ld_32(taddr + c0, g);
+            if (kBoth) tmem_ld_32(taddr + N_MAX + c0, reinterpret_cast<uint32_t(&)[32]>(u2));
             tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 8; ++q) {
               const float4 xs = xs4[c0 / 4 + q];
               acc_g[c0 + 4 * q] = fmaf(__uint_as_float(g[4 * q]), wsg * xs.x, acc_g[c0 + 4 * q]);
               acc_g[c0 + 4 * q + 1] = fmaf(__uint_as_float(g[4 * q + 1]), wsg * xs.y, acc_g[c0 + 4 * q + 1]);
@@ -396,15 +398,18 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
               acc_g[c0 + 4 * q + 3] = fmaf(__uint_as_float(g[4 * q + 3]), wsg * xs.w, acc_g[c0 + 4 * q + 3]);
             }
             if (kGateUp) {
-              tmem_ld_16(taddr + N_MAX + c0, g);
-              tmem_ld_wait();
+              if (!kBoth) {
+                tmem_ld_32(taddr + N_MAX + c0, g);
+                tmem_ld_wait();
+              }
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
+              for (int q = 0; q < 8; ++q) {
                 const float4 xs = xs4[c0 / 4 + q];
-                acc_u[c0 + 4 * q] = fmaf(__uint_as_float(g[4 * q]), wsu * xs.x, acc_u[c0 + 4 * q]);
-                acc_u[c0 + 4 * q + 1] = fmaf(__uint_as_float(g[4 * q + 1]), wsu * xs.y, acc_u[c0 + 4 * q + 1]);
-                acc_u[c0 + 4 * q + 2] = fmaf(__uint_as_float(g[4 * q + 2]), wsu * xs.z, acc_u[c0 + 4 * q + 2]);
-                acc_u[c0 + 4 * q + 3] = fmaf(__uint_as_float(g[4 * q + 3]), wsu * xs.w, acc_u[c0 + 4 * q + 3]);
+                const uint32_t* r = kBoth ? u2 : g;
+                acc_u[c0 + 4 * q] = fmaf(__uint_as_float(r[4 * q]), wsu * xs.x, acc_u[c0 + 4 * q]);
+                acc_u[c0 + 4 * q + 1] = fmaf(__uint_as_float(r[4 * q + 1]), wsu * xs.y, acc_u[c0 + 4 * q + 1]);
+                acc_u[c0 + 4 * q + 2] = fmaf(__uint_as_float(r[4 * q + 2]), wsu * xs.z, acc_u[c0 + 4 * q + 2]);
+                acc_u[c0 + 4 * q + 3] = fmaf(__uint_as_float(r[4 * q + 3]), wsu * xs.w, acc_u[c0 + 4 * q + 3]);
               }
             }
           }

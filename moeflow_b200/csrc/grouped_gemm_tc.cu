@@ -156,6 +156,15 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
   }
 }
 
+// One output element: bf16 (one rounding of the fp32 value), or fp32 as it is when the caller asked for it
+// (router logits from the down-projection kernel).
+__device__ __forceinline__ void store_out(const mf_gemm_args& a, long long index, float v) {
+  if (a.out_fp32)
+    static_cast<float*>(a.out)[index] = v;
+  else
+    static_cast<__nv_bfloat16*>(a.out)[index] = __float2bfloat16_rn(v);
+}
+
 template <bool kGateUp, int N_MAX, bool kReturn = false>
 __global__ void __launch_bounds__(kReturn ? kThreadsWithReturn : kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_b,
@@ -228,7 +237,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     grid_dep_launch();
   } else {
     grid_dep_launch();
-    if (warp >= 2) grid_dep_wait();  // token-operand producers (act rows) and epilogue (arrival counters)
+    // token-operand producers (act rows) and epilogue: after the whole gate/up grid, unless the activations
+    // are handed over tile by tile (tile_wait), in which case nothing here depends on that grid's completion
+    if (warp >= 2 && a.tile_wait == nullptr) grid_dep_wait();
   }
 
   if (trace && tid == 0) trace[1] = global_timer_ns();
@@ -352,7 +363,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       bool ok = true;
       WorkIter it = work;
       Seg sg;
+      int ready_tile = -1;
       while (ok && it.next(sg)) {
+        if (a.tile_wait != nullptr && sg.tt != ready_tile) {
+          // the tile's activations are final once every gate/up unit of the tile has reported its four quarters
+          bool got = true;
+          if (lane == 0) {
+            got = wait_count_ge_gpu(a.tile_wait + sg.tt, a.tile_wait_target, wait_ns);
+            fence_proxy_async_all();  // the TMA reads below come after the acquire
+          }
+          ok = __all_sync(0xffffffffu, got);
+          if (!ok) {
+            if (lane == 0) {
+              *abort_flag = 1;
+              report_status(a.status, kGemmFullTimeout, 6, blockIdx.x, 0);
+            }
+            break;
+          }
+          ready_tile = sg.tt;
+        }
         for (int j = 0; j < sg.nkb; ++j) {
           const int kb = sg.kb0 + j;
           ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
@@ -387,7 +416,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     bool ok = true;
     WorkIter it = work;
     Seg sg;
+    int ready_tile = -1;
     while (ok && it.next(sg)) {
+      if (a.tile_wait != nullptr && sg.tt != ready_tile) {
+        bool got = wait_count_ge_gpu(a.tile_wait + sg.tt, a.tile_wait_target, wait_ns);
+        ok = __all_sync(0xffffffffu, got);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report_status(a.status, kGemmFullTimeout, 6, blockIdx.x, 0);
+          }
+          break;
+        }
+        ready_tile = sg.tt;
+      }
       const int n_rows = sg.n_rows;
       int n_tile = (n_rows + 15) & ~15;
       if (n_tile < 16) n_tile = 16;
@@ -468,8 +510,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + acc.stage * Cfg::kAccCols;
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
       const long long out_col = (long long)mb * kBlockM + row;
+      const bool col_ok = a.out_cols <= 0 || out_col < a.out_cols;  // weight rows padded up to a block are not stored
 
       if (sg.nseg == 1) {
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
@@ -492,13 +534,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               } else if (a.row_scale) {
                 v *= a.row_scale[row_start + n];
               }
-              out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+              if (col_ok) store_out(a, (long long)(row_start + n) * a.out_pitch + out_col, v);
             }
           }
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
+        if (a.tile_done != nullptr) {
+          __threadfence();  // every lane's stores are visible device-wide before the count
+          __syncwarp();
+          if (lane == 0) atomicAdd(a.tile_done + sg.tt, 1);
+        }
         if (with_return) ok = enqueue_return(n_rows, row_start, mb);
       } else {
         // The unit is cut along K: park the fp32 partial sums, then the last quarter-warp to arrive adds
@@ -566,11 +613,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 } else if (a.row_scale) {
                   r *= a.row_scale[row_start + n];
                 }
-                out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(r);
+                if (col_ok) store_out(a, (long long)(row_start + n) * a.out_pitch + out_col, r);
               }
             }
           }
           if (lane == 0) a.counters[sg.unit * 4 + wq] = 0;
+          if (a.tile_done != nullptr) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(a.tile_done + sg.tt, 1);
+          }
           if (with_return) ok = enqueue_return(n_rows, row_start, mb);
         }
       }
@@ -659,6 +711,7 @@ static int check_args(const mf_gemm_args* a, int n_max, int grid) {
   if (a->m_blocks < 1 || a->k_blocks < 1) return -3;
   if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
   if (a->b_tmap != nullptr && a->b_index != nullptr) return -5;  // TMA token tiles need contiguous rows
+  if (a->ret_peer != nullptr && (a->out_fp32 || a->out_cols > 0)) return -6;  // the fused return path reads bf16 rows of full width
   return 0;
 }
 

@@ -76,6 +76,17 @@ typedef struct {
   long long partial_floats;  // floats in `partial`
   int n_counters;            // ints in `counters`
   int max_tiles;             // entries in tile_e / tile_s / tile_n
+  int out_fp32;              // bf16 kernels: 1 = `out` is fp32 [entries, out_pitch] (no rounding); not with ret_peer
+  int out_cols;              // bf16 kernels: > 0 = only output columns below this are stored (weight rows padded to 128)
+  // Tile-level hand-over from the gate/up GEMM to the down GEMM (bf16 kernels, both optional).  The gate/up
+  // kernel adds one to tile_done[tile] whenever a 32-row quarter of one of the tile's units has its final
+  // activations stored; the down kernel, given the same array as tile_wait, fetches a tile's activations as
+  // soon as the count reaches tile_wait_target (= 4 * the gate/up GEMM's m_blocks) instead of waiting for the
+  // whole gate/up grid, so SMs that the gate/up GEMM has left go straight on with down-projection units.
+  // The array must be zero before the gate/up kernel starts (mf_expert_meta clears it with the counters).
+  int* tile_done;
+  const int* tile_wait;
+  int tile_wait_target;
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
@@ -153,6 +164,7 @@ typedef struct {
   int* route_ids;
   int E, n_group, topk_group, sigmoid, renorm;
   float scale;
+  unsigned long long* trace; // optional [8] globaltimer stamps of CTA 0 (profiling aid), or NULL
 } mf_dispatch_args;
 int mf_dispatch_push(const mf_dispatch_args* args, mf_stream_t stream);
 
@@ -195,6 +207,7 @@ typedef struct {
   // 1: GEMMs with fewer than 8 units per CTA get the stream-K cut (plan word 0) when the scratch holds two
   // partial tiles per CTA; 0: always a K split from mf_plan_split.
   int stream_k;
+  unsigned long long* trace; // optional [8] globaltimer stamps of CTA 0 (profiling aid), or NULL
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 // The K-split rule of the metadata kernels, callable on the host (no device needed): the split in {1,2,4,8}
@@ -216,6 +229,7 @@ typedef struct {
   int R, C, H, K, rank;
   int valid_word;            // index of the valid flag among a row's int32 metadata words (2 * top_k)
   unsigned* push_epoch;      // local count of return pushes; the last CTA adds one (the combine's expectation)
+  unsigned long long* trace; // optional [8] globaltimer stamps of CTA 0 (profiling aid), or NULL
 } mf_reduce_push_args;
 int mf_owner_reduce_push(const mf_reduce_push_args* args, mf_stream_t stream);
 
@@ -229,6 +243,7 @@ typedef struct {
   int ring;                  // 1: order (rank+1 .. rank+R) % R with bf16 rounding after every add
   unsigned long long* status;
   unsigned long long wait_ns;
+  unsigned long long* trace; // optional [8] globaltimer stamps of CTA 0 (profiling aid), or NULL
 } mf_combine_args;
 int mf_combine(const mf_combine_args* args, mf_stream_t stream);
 

@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   const int row = blockIdx.x;  // = s*C + t
   const int s = row / a.C, t = row - s * a.C;
   const int tid = threadIdx.x;
+  unsigned long long* trace = (a.trace != nullptr && blockIdx.x == 0 && tid == 0) ? a.trace : nullptr;
+  if (trace) trace[0] = global_timer_ns();
   grid_dep_launch();
   // The valid flag and the inverse map were final before the GEMMs started (this grid can only be resident
   // once the down GEMM is, which follows the gate/up GEMM's wait for the metadata pass), so they are fetched
@@ -54,6 +56,7 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   const bool valid = __ldcg(meta + a.valid_word) != 0;
   if (valid && tid < a.K) s_pos[tid] = __ldcg(a.inv + (size_t)row * a.K + tid);
   grid_dep_wait();  // the down GEMM has completed: y is final
+  if (trace) trace[1] = global_timer_ns();
   if (valid) {
     __syncthreads();
     const int chunks = a.H / 8;
@@ -82,8 +85,10 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   // The barrier orders every thread's stores before thread 0's fence, which is cumulative: one system
   // fence per CTA instead of one per thread; then this row's arrival at its source rank.
   __syncthreads();
+  if (trace) trace[2] = global_timer_ns();  // row stored
   if (tid == 0) {
-    __threadfence_system();
+    fence_before_arrival(a.R);
+    if (trace) trace[3] = global_timer_ns();  // fenced
     red_add_relaxed_sys_u32(reinterpret_cast<unsigned*>(a.peer_flag[s]) + a.rank, 1u);
     // Off the critical path: the last CTA counts this push locally.  The combine of this rank expects
     // push_epoch * C arrivals from every owner (all ranks run the same sequence of launches, so their push
@@ -92,6 +97,7 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
     if (done == gridDim.x - 1) {
       *a.done_counter = 0u;
       if (a.push_epoch != nullptr) *a.push_epoch += 1u;
+      if (a.trace) a.trace[5] = global_timer_ns();  // last CTA done
     }
   }
 }
@@ -102,8 +108,11 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
   const int tid = threadIdx.x;
   // hit[t, :] was written by this rank's dispatch kernel: pull its line into L2 ahead of the wait (a hint only,
   // the values are read after the wait), so that the read below does not go to DRAM.
+  unsigned long long* trace = (a.trace != nullptr && blockIdx.x == 0 && tid == 0) ? a.trace : nullptr;
+  if (trace) trace[0] = global_timer_ns();
   if (tid == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.hit + (size_t)t * a.R));
   grid_dep_wait();
+  if (trace) trace[1] = global_timer_ns();
   if (tid < a.R) s_hit[tid] = __ldcg(a.hit + (size_t)t * a.R + tid);
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
   // counting flags: every owner adds one per received row of this rank (C of them) in every forward
@@ -111,6 +120,7 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
     if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)a.C, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);
   }
   __syncthreads();
+  if (trace) trace[2] = global_timer_ns();  // return flags seen
   const int chunks = a.H / 8;
   const uint4* ret = static_cast<const uint4*>(a.ret);
   uint4* out = static_cast<uint4*>(a.out) + (size_t)t * chunks;
@@ -139,6 +149,7 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
     }
     out[c] = pack_bf16x8(acc);
   }
+  if (trace) trace[3] = global_timer_ns();  // row written
 }
 
 // Peer ping used by the runtime tests: store a value into every peer's word [rank], then wait

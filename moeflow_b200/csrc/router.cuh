@@ -33,6 +33,14 @@ __device__ __forceinline__ Best warp_argmax(Best b) {
   return b;
 }
 
+constexpr int kRouteRegs = 16;  // experts per lane kept in registers (E <= 512); larger E selects from shared memory
+
+// Maps a float to an unsigned key with the same order (-inf lowest, +inf highest among non-NaN values).
+__device__ __forceinline__ unsigned float_order_key(float x) {
+  const unsigned u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 struct RouteParams {
   int E, K, n_group, topk_group, sigmoid, renorm;
   float scale;
@@ -94,24 +102,60 @@ __device__ __forceinline__ void route_token_warp(const float* __restrict__ lg, c
   float wsum = 0.f;
   float my_w = 0.f;  // lane k keeps the weight of slot k (K <= 32)
   int my_id = 0;
-  for (int k = 0; k < p.K; ++k) {
-    Best b{-CUDART_INF_F, -1};
-    for (int e = lane; e < E; e += 32) {
-      const float v = biased[e];
-      if (better(v, e, b.v, b.id)) {
-        b.v = v;
-        b.id = e;
+  if (E <= 32 * kRouteRegs) {
+    // Selection out of registers: lane l holds experts l, l + 32, ...; a round is a scan of the lane's own
+    // values, one warp-wide max over order-preserving integer keys and one warp-wide min over the ids that
+    // carry that maximum (ties go to the lower id), instead of ten dependent shuffles.
+    float v[kRouteRegs];
+#pragma unroll
+    for (int j = 0; j < kRouteRegs; ++j) {
+      const int e = lane + 32 * j;
+      v[j] = e < E ? biased[e] : -CUDART_INF_F;
+    }
+    for (int k = 0; k < p.K; ++k) {
+      unsigned bk = 0u;
+      int bj = 0;
+#pragma unroll
+      for (int j = 0; j < kRouteRegs; ++j) {
+        const unsigned key = (lane + 32 * j < E) ? float_order_key(v[j]) : 0u;  // padding never beats a real entry
+        if (key > bk) {  // strictly greater: the lowest index (lowest id of this lane) keeps a tie
+          bk = key;
+          bj = j;
+        }
       }
+      const unsigned wmax = __reduce_max_sync(0xffffffffu, bk);
+      const unsigned cand = (bk == wmax && bk != 0u) ? (unsigned)(lane + 32 * bj) : 0xffffffffu;
+      const int id = (int)__reduce_min_sync(0xffffffffu, cand);
+      const float w = score[id];
+      wsum += w;
+      if (lane == k) {
+        my_w = w;
+        my_id = id;
+      }
+#pragma unroll
+      for (int j = 0; j < kRouteRegs; ++j)
+        if (lane == (id & 31) && j == (id >> 5)) v[j] = -CUDART_INF_F;
     }
-    b = warp_argmax(b);
-    const float w = score[b.id];
-    wsum += w;
-    if (lane == k) {
-      my_w = w;
-      my_id = b.id;
+  } else {
+    for (int k = 0; k < p.K; ++k) {
+      Best b{-CUDART_INF_F, -1};
+      for (int e = lane; e < E; e += 32) {
+        const float v = biased[e];
+        if (better(v, e, b.v, b.id)) {
+          b.v = v;
+          b.id = e;
+        }
+      }
+      b = warp_argmax(b);
+      const float w = score[b.id];
+      wsum += w;
+      if (lane == k) {
+        my_w = w;
+        my_id = b.id;
+      }
+      if (lane == (b.id & 31)) biased[b.id] = -CUDART_INF_F;
+      __syncwarp();
     }
-    if (lane == (b.id & 31)) biased[b.id] = -CUDART_INF_F;
-    __syncwarp();
   }
   if (p.renorm) my_w = my_w / (wsum + 1e-20f);
   out_w = my_w * p.scale;

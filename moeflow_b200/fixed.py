@@ -451,12 +451,17 @@ class FixedEPLayer:
         mb1, mb2 = I // 128, H // 128
         # arrival counters of cut units: one per (unit, 32-row quarter) and, in the fp8 kernels with 128-column
         # tiles, per column group (two)
-        self._counters1 = torch.zeros(self.max_tiles * mb1 * 8, **i32)
+        n_cnt1 = self.max_tiles * mb1 * 8
+        # the tail of the first counter array (cleared with it by the metadata kernel) counts, per token tile, the
+        # gate/up quarters whose activations are final: the down GEMM starts a tile as soon as it is complete
+        self._counters1 = torch.zeros(n_cnt1 + self.max_tiles, **i32)
+        self._tile_done = self._counters1[n_cnt1:]
         self._counters2 = torch.zeros(self.max_tiles * mb2 * 8, **i32)
         # split-K scratch: a byte budget; the metadata kernel sizes the partial slots for the widest token tile
-        partial_floats = int(self.gemm_kwargs.get("split_scratch_mb", 64)) * (1 << 20) // 4
+        # (each GEMM gets its own half: the down GEMM may run while gate/up units are still being fixed up)
+        partial_floats = int(self.gemm_kwargs.get("split_scratch_mb", 64)) * (1 << 20) // 4 // 2
         self.max_split_slots = partial_floats // (2 * self.block_m * 128)
-        self._partial = torch.zeros(partial_floats, dtype=torch.float32, device=dev)
+        self._partial = torch.zeros(2 * partial_floats, dtype=torch.float32, device=dev)
         self._keep: list = []  # ctypes objects and temporaries that must outlive launches
 
         S = _lib
@@ -485,8 +490,8 @@ class FixedEPLayer:
         # Metadata: one CTA for decode sizes; for prefill sizes (many received rows) the counting sort is
         # split over several CTAs in two chained launches.  Same result either way.
         n_words = R * Cc * K
-        # measured on B200: the single CTA takes 10 / 14 / 20 / 32 / 134 us at 1024 / 2048 / 4096 / 8192 / 32768
-        # slot words, the two chained multi-CTA launches 11-18 us throughout
+        # up to 8192 slot words one CTA keeps them all in registers (one pass); above that the two chained
+        # multi-CTA launches take 11-18 us where a sweeping single CTA would take 134 us at 32768 words
         self.meta_ctas = int(self.gemm_kwargs.get("meta_ctas", choose_meta_ctas(n_words, self.n_sms)))
         if not 1 <= self.meta_ctas <= 1024:
             raise ValueError("meta_ctas must be between 1 and 1024")
@@ -507,7 +512,7 @@ class FixedEPLayer:
             b_base=self._recv_store.data_ptr(), b_pitch=self.pitch * 2, b_index=self.entry_row.data_ptr(),
             split_word=S.PLAN_SPLIT1, m_blocks=mb1, k_blocks=H // 64, rows_per_expert=2 * I, up_row_offset=I,
             out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=self._counters1.data_ptr(),
-            n_counters=self._counters1.numel(), **common,
+            n_counters=n_cnt1, **common,
         )
         self._a_gemm2 = S.GemmArgs(
             b_base=self.act.data_ptr(), b_pitch=I * 2, b_index=None, split_word=S.PLAN_SPLIT2, m_blocks=mb2,
@@ -515,6 +520,14 @@ class FixedEPLayer:
             row_scale=self.entry_w.data_ptr(), counters=self._counters2.data_ptr(),
             n_counters=self._counters2.numel(), **common,
         )
+        self._a_gemm2.partial = self._partial[partial_floats:].data_ptr()
+        # Tile-level hand-over of the activations (gemm_kwargs tile_handover=False: the down GEMM waits for the
+        # whole gate/up grid instead).
+        self.tile_handover = bool(self.gemm_kwargs.get("tile_handover", True))
+        if self.tile_handover:
+            self._a_gemm1.tile_done = self._tile_done.data_ptr()
+            self._a_gemm2.tile_wait = self._tile_done.data_ptr()
+            self._a_gemm2.tile_wait_target = 4 * mb1
         # The down GEMM reads its token operand (act, contiguous in expert-major order) by TMA, one bulk copy
         # per pipeline stage; gemm_kwargs b_tma=False falls back to the 16-byte gather the gate/up GEMM uses.
         self._tmap_act = None
@@ -596,12 +609,17 @@ class FixedEPLayer:
         received rows and the SwiGLU activations per 1x128 group on the device and runs the
         ``kind::f8f6f4`` grouped GEMMs; inputs and outputs of the layer stay bf16.
         """
-        from .ops import _lib
+        self.bind_weights_fp8(self.make_fp8_pack(w13_q, w13_s, w2_q, w2_s))
+
+    def make_fp8_pack(self, w13_q, w13_s, w2_q, w2_s) -> dict:
+        """Validate one MoE layer's e4m3 weights and build what binding them needs (TMA descriptors, fp32 scale
+        tensors).  Build once per MoE layer, then ``bind_weights_fp8(pack)`` before its forward: a decoder
+        shares one buffer set between all its MoE layers."""
         from .ops.kernels import make_weight_tmap
 
         if self.backend != "cuda":
             raise ValueError("fp8 weights need the cuda backend")
-        L, H, I, N = self.L, self.H, self.I, self.n_entries
+        L, H, I = self.L, self.H, self.I
         if tuple(w13_q.shape) != (L, 2 * I, H) or tuple(w2_q.shape) != (L, H, I):
             raise ValueError("weight shard has the wrong shape")
         if w13_q.dtype != torch.float8_e4m3fn or w2_q.dtype != torch.float8_e4m3fn:
@@ -610,12 +628,21 @@ class FixedEPLayer:
             raise ValueError("scales must be one fp32 per 128x128 block")
         if H > 4096 or I > 4096:
             raise ValueError("fp8 path supports K <= 4096")
-        dev = self.device
-        f = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
-             "s2": w2_s.to(torch.float32).contiguous()}
-        f["tm13"] = make_weight_tmap(f["w13"].view(torch.uint8))
-        f["tm2"] = make_weight_tmap(f["w2"].view(torch.uint8))
+        pack = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
+                "s2": w2_s.to(torch.float32).contiguous()}
+        pack["tm13"] = make_weight_tmap(pack["w13"].view(torch.uint8))
+        pack["tm2"] = make_weight_tmap(pack["w2"].view(torch.uint8))
+        return pack
+
+    def _fp8_buffers(self) -> dict:
+        """Quantised activations and the fp8 GEMM argument blocks of this buffer set (allocated on first use)."""
+        if getattr(self, "_fp8_shared", None) is not None:
+            return self._fp8_shared
+        from .ops import _lib
+
+        H, I, N, dev = self.H, self.I, self.n_entries, self.device
         rows = self.world * self.C
+        f = {}
         f["xq"] = torch.zeros(rows, H, dtype=torch.uint8, device=dev)
         f["xs"] = torch.zeros(rows, H // 128, dtype=torch.float32, device=dev)
         f["aq"] = torch.zeros(max(N, self.block_m), I, dtype=torch.uint8, device=dev)  # >= one TMA box of rows
@@ -627,18 +654,29 @@ class FixedEPLayer:
         f["a1"] = _lib.GemmArgs(b_base=f["xq"].data_ptr(), b_pitch=H, b_index=self.entry_row.data_ptr(),
                                 split_word=_lib.PLAN_SPLIT1, m_blocks=I // 128, k_blocks=H // 128, rows_per_expert=2 * I,
                                 up_row_offset=I, out=self.act.data_ptr(), out_pitch=I, row_scale=None, counters=g1.counters,
-                                n_counters=g1.n_counters, w_scale=f["s13"].data_ptr(), b_scale=f["xs"].data_ptr(), b_scale_pitch=H // 128, **common)
+                                n_counters=g1.n_counters, w_scale=None, b_scale=f["xs"].data_ptr(), b_scale_pitch=H // 128,
+                                **common)
         f["a2"] = _lib.GemmArgs(b_base=f["aq"].data_ptr(), b_pitch=I, b_index=None, split_word=_lib.PLAN_SPLIT2,
                                 m_blocks=H // 128, k_blocks=I // 128, rows_per_expert=H, up_row_offset=0,
                                 out=self.y.data_ptr(), out_pitch=H, row_scale=self.entry_w.data_ptr(), counters=g2.counters,
-                                n_counters=g2.n_counters, w_scale=f["s2"].data_ptr(), b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128, **common)
+                                n_counters=g2.n_counters, w_scale=None, b_scale=f["as"].data_ptr(), b_scale_pitch=I // 128,
+                                **common)
         if bool(self.gemm_kwargs.get("b_tma", True)):
             from .ops.kernels import make_tile_tmap
 
             f["tm_aq"] = make_tile_tmap(f["aq"], self.block_m)  # the down GEMM reads its e4m3 token tiles by TMA
             f["a2"].b_tmap = C.addressof(f["tm_aq"])
+        self._fp8_shared = f
+        return f
+
+    def bind_weights_fp8(self, pack: dict) -> None:
+        """Point this (possibly shared) buffer set at one MoE layer's e4m3 weights; no copies."""
+        f = self._fp8_buffers()
+        f["a1"].w_scale, f["a2"].w_scale = pack["s13"].data_ptr(), pack["s2"].data_ptr()
+        f["tm13"], f["tm2"], f["pack"] = pack["tm13"], pack["tm2"], pack
         self._fp8 = f
-        self._tmap13, self._tmap2 = f["tm13"], f["tm2"]
+        self.w13, self.w2 = pack["w13"], pack["w2"]
+        self._tmap13, self._tmap2 = pack["tm13"], pack["tm2"]
 
     def make_weight_maps(self, w13_local: torch.Tensor, w2_local: torch.Tensor):
         """TMA descriptors for a weight pair (build once per MoE layer, then pass to ``bind_weights``)."""
@@ -783,9 +821,9 @@ def choose_block_m(capacity: int, top_k: int, local_experts: int) -> int:
 
 
 def choose_meta_ctas(slot_words: int, n_sms: int) -> int:
-    """CTAs of the metadata pass for ``rows * K`` received slot words: one below 2048, else one per 128 words
-    up to one per SM."""
-    return 1 if slot_words < 2048 else max(2, min(n_sms, (slot_words + 127) // 128))
+    """CTAs of the metadata pass for ``rows * K`` received slot words: one up to 8192 (the single CTA then keeps
+    every slot word in registers and needs one pass), else one per 128 words up to one per SM."""
+    return 1 if slot_words <= 8192 else max(2, min(n_sms, (slot_words + 127) // 128))
 
 
 def _cuda_ok(cfg: MoEConfig) -> bool:

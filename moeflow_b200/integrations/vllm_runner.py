@@ -257,19 +257,36 @@ class RunnerCore:
             self._local_kernel = mk.FusedMoEKernel(MoEPrepareAndFinalizeNoDPEPModular(), experts)
         return self._local_kernel
 
-    def _use_native_experts(self, layer) -> bool:
+    def _use_native_experts(self, layer) -> str | None:
+        """Which of this framework's own expert kernels can run the layer's weights: ``"bf16"``, ``"fp8"`` (e4m3
+        weights with one fp32 ``weight_scale_inv`` per 128x128 block, the GLM-5.3-Flash FP8 checkpoint layout:
+        activations are quantised per 1x128 group on the device) or None (the engine's fused experts run)."""
         choice = self.moeflow.experts
         if choice == "vllm" or layer.backend != "cuda":
-            return False
-        w13 = getattr(self.routed_experts, "w13_weight", None)
-        w2 = getattr(self.routed_experts, "w2_weight", None)
-        fits = (
-            w13 is not None and w2 is not None and w13.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16
+            return None
+        experts = self.routed_experts
+        w13 = getattr(experts, "w13_weight", None)
+        w2 = getattr(experts, "w2_weight", None)
+        shapes = (
+            w13 is not None and w2 is not None
             and tuple(w13.shape) == (layer.L, 2 * layer.I, layer.H) and tuple(w2.shape) == (layer.L, layer.H, layer.I)
         )
-        if choice == "native" and not fits:
-            raise ValueError("MOEFLOW_EXPERTS=native needs bf16 w13 [L, 2I, H] and w2 [L, H, I] expert weights")
-        return fits
+        kind = None
+        if shapes and w13.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16:
+            kind = "bf16"
+        elif shapes and w13.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn:
+            s13 = getattr(experts, "w13_weight_scale_inv", None)
+            s2 = getattr(experts, "w2_weight_scale_inv", None)
+            if (
+                s13 is not None and s2 is not None and layer.H <= 4096 and layer.I <= 4096
+                and tuple(s13.shape) == (layer.L, 2 * layer.I // 128, layer.H // 128)
+                and tuple(s2.shape) == (layer.L, layer.H // 128, layer.I // 128)
+            ):
+                kind = "fp8"
+        if choice == "native" and kind is None:
+            raise ValueError("MOEFLOW_EXPERTS=native needs bf16 expert weights w13 [L, 2I, H] / w2 [L, H, I], or e4m3 "
+                             "weights of those shapes with fp32 weight_scale_inv per 128x128 block")
+        return kind
 
     def _apply_fixed(self, hidden_states, router_logits, shared_experts_input, input_ids, overlapping, capacity):
         self._moeflow_fixed_calls += 1
@@ -285,7 +302,14 @@ class RunnerCore:
             raise ValueError("BF16 Ring compatibility requires BF16 hidden states")
         combine_fn = make_combine_fn(self.moeflow.combine_mode, group.rank_in_group)
         native = self._use_native_experts(layer)
-        if native:
+        if native == "fp8":
+            # the block-scaled e4m3 weights stay as the engine loaded them; descriptors are built once per MoE layer
+            if self._native_tmaps is None:
+                self._native_tmaps = layer.make_fp8_pack(experts.w13_weight, experts.w13_weight_scale_inv,
+                                                         experts.w2_weight, experts.w2_weight_scale_inv)
+            layer.bind_weights_fp8(self._native_tmaps)
+            out = layer.forward_routed(hidden_states, weights, ids, combine_fn=combine_fn)
+        elif native:
             if self._native_tmaps is None:
                 self._native_tmaps = layer.make_weight_maps(experts.w13_weight, experts.w2_weight)
             layer.bind_weights(experts.w13_weight, experts.w2_weight, *self._native_tmaps)
@@ -317,7 +341,8 @@ class RunnerCore:
                 "intercepted": True, "mode": "fixed", "tokens": int(hidden_states.shape[0]), "capacity": capacity,
                 "combine_mode": self.moeflow.combine_mode, "fused_dispatch": self.moeflow.fused_dispatch,
                 "fused_expert_prep": self.moeflow.fused_expert_prep,
-                "direct_expert_output": self.moeflow.direct_expert_output, "experts": "native" if native else "vllm",
+                "direct_expert_output": self.moeflow.direct_expert_output,
+                "experts": f"native-{native}" if native else "vllm",
             })
         return self._shared_output(overlapping, out)
 

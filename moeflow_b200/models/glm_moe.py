@@ -5,7 +5,7 @@ DP = EP = world):
 
 ``SharedExpert``   the always-on SwiGLU MLP, run through the same tcgen05 grouped GEMM kernels as the
                    routed experts with a static one-expert plan;
-``MoEBlock``       RMSNorm (sm_100a kernel) -> router logits (plain library GEMM, fp32 output) ->
+``MoEBlock``       RMSNorm (sm_100a kernel) -> router logits (``RouterLogits``: the tcgen05 grouped kernel, fp32 output) ->
                    routed experts (``FixedEPLayer``: fused route+dispatch, expert GEMMs, return push,
                    combine) + shared expert -> residual;
 ``Attention``      grouped-query attention over a static KV cache for single-token decode steps, with
@@ -107,16 +107,69 @@ class SharedExpert:
         return self.out[:t]
 
 
+class RouterLogits:
+    """Router logits ``h . gate_w^T`` as fp32 ``[T, E]`` on the grouped down-projection kernel (tcgen05, bf16
+    operands, fp32 accumulation and fp32 output): the gate matrix is one "expert" whose rows are padded to a
+    multiple of 128, K is split so that the few weight blocks spread over several SMs, and only the E real
+    columns are stored.  With it the MoE block issues no library GEMM."""
+
+    def __init__(self, gate_w: torch.Tensor, capacity: int, block_m: int = 64):
+        from ..ops import _lib
+        from ..ops.grouped_gemm import plan_from_offsets
+        from ..ops.kernels import make_weight_tmap, sm_count
+
+        E, H = gate_w.shape
+        dev = gate_w.device
+        if H % 64:
+            raise ValueError("hidden size must be a multiple of 64")
+        self._lib, self.E, self.H, self.C, self.block_m = _lib, E, H, capacity, block_m
+        rows = (E + 127) // 128 * 128
+        self.w = torch.zeros(1, rows, H, dtype=torch.bfloat16, device=dev)
+        self.w[0, :E] = gate_w.to(torch.bfloat16)
+        self.n_sms = sm_count(dev.index or 0)
+        k_blocks = H // 64
+        split = max(s for s in (1, 2, 4, 8) if k_blocks % s == 0 and k_blocks // s >= 2 or s == 1)
+        self.tp = plan_from_offsets([0, capacity], block_m, dev, split2=split)
+        m_blocks = rows // 128
+        slots = self.tp.n_tiles * m_blocks * split
+        self._x = torch.zeros(max(capacity, block_m), H, dtype=torch.bfloat16, device=dev)
+        self.logits = torch.zeros(capacity, E, dtype=torch.float32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int64, device=dev)
+        self._scratch = torch.zeros(max(1, slots) * block_m * 128, dtype=torch.float32, device=dev)
+        self._counters = torch.zeros(self.tp.n_tiles * m_blocks * 8, dtype=torch.int32, device=dev)
+        self._tmap = make_weight_tmap(self.w)
+        self._args = _lib.GemmArgs(
+            b_base=self._x.data_ptr(), b_pitch=H * 2, b_index=None, tile_e=self.tp.tile_e.data_ptr(),
+            tile_s=self.tp.tile_s.data_ptr(), tile_n=self.tp.tile_n.data_ptr(), plan=self.tp.plan.data_ptr(),
+            split_word=_lib.PLAN_SPLIT2, m_blocks=m_blocks, k_blocks=k_blocks, rows_per_expert=rows, up_row_offset=0,
+            out=self.logits.data_ptr(), out_pitch=E, row_scale=None, partial=self._scratch.data_ptr(),
+            counters=self._counters.data_ptr(), max_split_slots=slots, limit=0.0, round_h=0, status=self.status.data_ptr(),
+            wait_ns=2_000_000_000, partial_floats=self._scratch.numel(), n_counters=self._counters.numel(),
+            max_tiles=self.tp.tile_e.numel(), out_fp32=1, out_cols=E,
+        )
+
+    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+        t = h.shape[0]
+        self._x[:t].copy_(h)
+        self._lib.check(self._lib.lib().mf_gemm_down(self._tmap, C.byref(self._args), self.block_m, self.n_sms,
+                                                     self._lib.stream_ptr()), "router logits")
+        return self.logits[:t]
+
+
 class MoEBlock:
     """Pre-norm MoE block: ``x + routed(norm(x)) + shared(norm(x))``."""
 
     def __init__(self, cfg: MoEConfig, routed: FixedEPLayer, gate_w: torch.Tensor, bias: torch.Tensor | None,
-                 norm_w: torch.Tensor, shared: SharedExpert | None, eps: float = 1e-6):
+                 norm_w: torch.Tensor, shared: SharedExpert | None, eps: float = 1e-6, router: RouterLogits | None = None):
         self.cfg, self.routed, self.gate_w, self.bias, self.norm_w, self.shared, self.eps = cfg, routed, gate_w, bias, norm_w, shared, eps
+        self.router = router
 
     def __call__(self, x: torch.Tensor, num_valid: torch.Tensor | None = None) -> torch.Tensor:
         h = _rmsnorm(x, self.norm_w, self.eps)
-        logits = torch.matmul(h.to(self.gate_w.dtype), self.gate_w.transpose(0, 1)).to(torch.float32)
+        if self.router is not None:
+            logits = self.router(h)
+        else:
+            logits = torch.matmul(h.to(self.gate_w.dtype), self.gate_w.transpose(0, 1)).to(torch.float32)
         routed = self.routed.forward(h, logits, self.bias, num_valid)[: x.shape[0]]
         out = x + routed
         if self.shared is not None:
@@ -166,7 +219,11 @@ class DecodeModel:
     """``n_layers`` decoder layers for a fixed per-rank batch; ``step()`` runs one decode step from a graph."""
 
     def __init__(self, cfg: MoEConfig, rank: int, world: int, batch: int, n_layers: int, device, acfg: AttentionConfig | None = None,
-                 group=None, seed: int = 0, attention: bool = True, weights_factory=None):
+                 group=None, seed: int = 0, attention: bool = True, weights_factory=None, fp8: bool = False,
+                 own_router_gemm: bool = True):
+        """``fp8``: the routed experts are kept as block-scaled e4m3 (one fp32 scale per 128x128 block, quantised
+        from the random bf16 weights) and run on the ``kind::f8f6f4`` grouped GEMMs.  ``own_router_gemm``: router
+        logits on the tcgen05 grouped kernel instead of a library matmul."""
         self.cfg, self.rank, self.world, self.batch, self.device = cfg, rank, world, batch, torch.device(device)
         self.acfg = acfg or AttentionConfig()
         dev, H, I, L = self.device, cfg.hidden_size, cfg.moe_intermediate_size, cfg.experts_per_rank(world)
@@ -190,8 +247,23 @@ class DecodeModel:
                 for e in range(L):
                     w13[e] = randn(2 * I, H, scale=2.0 / math.sqrt(H))
                     w2[e] = randn(H, I, scale=1.0 / math.sqrt(I))
-            maps = self.routed.make_weight_maps(w13, w2)
+            pack = None
+            if fp8:
+                from ..weights import quant_block_fp8
+
+                def quantise(w):
+                    qs, ss = zip(*(quant_block_fp8(w[e]) for e in range(w.shape[0])))
+                    return torch.stack([q.view(torch.uint8) for q in qs]).view(torch.float8_e4m3fn), torch.stack(ss)
+
+                q13, s13 = quantise(w13)
+                q2, s2 = quantise(w2)
+                pack = self.routed.make_fp8_pack(q13, s13, q2, s2)
+                w13 = w2 = None  # only the e4m3 copies are kept
+                maps = (None, None)
+            else:
+                maps = self.routed.make_weight_maps(w13, w2)
             gate_w = randn(cfg.n_routed_experts, H, scale=1.0 / math.sqrt(H)).to(torch.float32)
+            router = RouterLogits(gate_w, capacity) if own_router_gemm else None
             bias = 0.05 * torch.randn(cfg.n_routed_experts, generator=g, device=dev)
             shared = None
             if cfg.n_shared_experts:
@@ -200,8 +272,8 @@ class DecodeModel:
                                       capacity, cfg.swiglu_limit)
             norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
             attn = Attention(H, self.acfg, batch, dev, seed * 31 + layer) if attention else None
-            self.layers.append({"w13": w13, "w2": w2, "maps": maps, "gate_w": gate_w, "bias": bias, "shared": shared,
-                                "norm_w": norm_w, "attn": attn})
+            self.layers.append({"w13": w13, "w2": w2, "maps": maps, "fp8": pack, "gate_w": gate_w, "bias": bias,
+                                "shared": shared, "norm_w": norm_w, "attn": attn, "router": router})
         self.x = torch.zeros(batch, H, dtype=torch.bfloat16, device=dev)
         self.out = torch.zeros_like(self.x)
         self.pos = torch.zeros((), dtype=torch.int64, device=dev)
@@ -221,8 +293,12 @@ class DecodeModel:
         for layer in self.layers:
             if layer["attn"] is not None:
                 x = layer["attn"](x, self.pos, self.mask)
-            self.routed.bind_weights(layer["w13"], layer["w2"], *layer["maps"])
-            block = MoEBlock(self.cfg, self.routed, layer["gate_w"], layer["bias"], layer["norm_w"], layer["shared"])
+            if layer["fp8"] is not None:
+                self.routed.bind_weights_fp8(layer["fp8"])
+            else:
+                self.routed.bind_weights(layer["w13"], layer["w2"], *layer["maps"])
+            block = MoEBlock(self.cfg, self.routed, layer["gate_w"], layer["bias"], layer["norm_w"], layer["shared"],
+                             router=layer["router"])
             x = block(x)
         self.out.copy_(x)
 

@@ -73,6 +73,11 @@ class GemmArgs(C.Structure):
         ("partial_floats", C.c_longlong),
         ("n_counters", C.c_int),
         ("max_tiles", C.c_int),
+        ("out_fp32", C.c_int),
+        ("out_cols", C.c_int),
+        ("tile_done", C.c_void_p),
+        ("tile_wait", C.c_void_p),
+        ("tile_wait_target", C.c_int),
     ]
 
 
@@ -106,6 +111,7 @@ class DispatchArgs(C.Structure):
         ("sigmoid", C.c_int),
         ("renorm", C.c_int),
         ("scale", C.c_float),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -149,6 +155,7 @@ class MetaArgs(C.Structure):
         ("cta_hist", C.c_void_p),
         ("acc", C.c_void_p),
         ("stream_k", C.c_int),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -169,6 +176,7 @@ class ReducePushArgs(C.Structure):
         ("rank", C.c_int),
         ("valid_word", C.c_int),
         ("push_epoch", C.c_void_p),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -186,6 +194,7 @@ class CombineArgs(C.Structure):
         ("ring", C.c_int),
         ("status", C.c_void_p),
         ("wait_ns", C.c_ulonglong),
+        ("trace", C.c_void_p),
     ]
 
 

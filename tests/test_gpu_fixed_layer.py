@@ -106,6 +106,40 @@ def test_expert_meta_matches_torch_layout(world, cap, meta_ctas):
         assert plan[5] == live_rows  # rows with at least one local slot
 
 
+@pytest.mark.parametrize("world,cap,experts,top_k", [(2, 256, 24, 6), (1, 1024, 32, 8), (4, 100, 36, 3), (8, 128, 64, 8)])
+def test_one_pass_metadata_kernel_at_decode_sizes(world, cap, experts, top_k):
+    """The register-resident single-CTA kernel (up to 8192 slot words) against the torch layout: top-k that is
+    and is not a power of two (row hit counts by ballot or from the rows), full 8-step batches, ragged ends."""
+    cfg = replace(SMALL_GPU, n_routed_experts=experts, top_k=top_k)
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    tokens = [cap, cap // 2, 1, 0, cap - 1, 3, cap, 7][:world]
+    xs, lgs = _inputs(cfg, world, tokens, 13)
+    cu = _layers(cfg, world, cap, w13, w2, "cuda")
+    assert cu[0].meta_ctas == 1 and world * cap * top_k <= 8192
+    for rep in range(2):
+        for ly, x, lg in zip(cu, xs, lgs):
+            ly.stage_pack(x, lg, None)
+        for ly in cu:
+            ly._cuda_meta()
+            torch.cuda.synchronize()
+            _ok(ly)
+            _, local, wts = ly.received_routing()
+            order, offsets, inv, entry_row, entry_slot = ly._torch_layout(local)
+            n = int(offsets[-1])
+            assert torch.equal(ly.offsets.long(), offsets)
+            assert torch.equal(ly.entry_row[:n].long(), entry_row[:n])
+            assert torch.equal(ly.entry_slot[:n].long(), entry_slot[:n])
+            assert torch.equal(ly.inv.long(), inv)
+            assert torch.equal(ly.entry_w[:n], wts[entry_row[:n], entry_slot[:n]])
+            assert torch.equal(ly.row_hits.long(), (local >= 0).sum(-1))
+            plan = ly.plan.tolist()
+            assert plan[3] == n and plan[5] == int((local >= 0).any(dim=-1).sum())
+            counts = (offsets[1:] - offsets[:-1]).tolist()
+            tiles = [(e, int(offsets[e]) + s, min(ly.block_m, c - s)) for e, c in enumerate(counts) for s in range(0, c, ly.block_m)]
+            assert plan[0] == len(tiles)
+            assert list(zip(ly.tile_e[: plan[0]].tolist(), ly.tile_s[: plan[0]].tolist(), ly.tile_n[: plan[0]].tolist())) == tiles
+
+
 def test_multi_cta_metadata_equals_the_single_cta_kernel_at_prefill_size():
     """2048 tokens on one rank (16384 slot words): every output array and the plan are identical, and a
     second forward (the scratch counter must have been left at zero) is identical again."""

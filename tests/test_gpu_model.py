@@ -48,3 +48,44 @@ def test_decode_model_steps_and_matches_eager():
         out = model.step()
     assert int(model.pos) == 22 and torch.isfinite(out.float()).all()
     model.close()
+
+
+@pytest.mark.parametrize("experts,hidden,capacity,tokens", [(288, 512, 8, 5), (16, 512, 128, 128), (130, 1024, 64, 64)])
+def test_router_logits_on_the_grouped_kernel_match_fp32(experts, hidden, capacity, tokens):
+    """fp32 logits from the tcgen05 down-projection kernel (bf16 operands, fp32 accumulation, fp32 store, expert
+    count not a multiple of 128) against an fp32 matmul of the same bf16 values."""
+    from moeflow_b200.models.glm_moe import RouterLogits
+
+    g = torch.Generator().manual_seed(3)
+    gate = (torch.randn(experts, hidden, generator=g) / hidden**0.5).cuda()
+    h = torch.randn(tokens, hidden, generator=g).bfloat16().cuda()
+    router = RouterLogits(gate, capacity)
+    guard = router.logits.clone()
+    out = router(h).clone()
+    torch.cuda.synchronize()
+    assert int(router.status.item()) == 0
+    assert out.dtype == torch.float32 and tuple(out.shape) == (tokens, experts)
+    ref = h.float() @ gate.bfloat16().float().t()
+    assert (out - ref).abs().max() <= 1e-3 * ref.abs().max() + 1e-4
+    assert torch.equal(router.logits[tokens:], guard[tokens:])  # rows past the batch are not touched
+
+
+def test_decode_model_with_fp8_experts_steps():
+    from moeflow_b200.models.glm_moe import AttentionConfig, DecodeModel
+
+    acfg = AttentionConfig(n_heads=8, n_kv_heads=2, head_dim=64, max_seq=64)
+    bf16 = DecodeModel(CFG, 0, 1, batch=4, n_layers=2, device="cuda", acfg=acfg, seed=5)
+    fp8 = DecodeModel(CFG, 0, 1, batch=4, n_layers=2, device="cuda", acfg=acfg, seed=5, fp8=True)
+    x = torch.randn(4, CFG.hidden_size, generator=torch.Generator().manual_seed(2)).bfloat16()
+    outs = []
+    for model in (bf16, fp8):
+        model.prefill_standin(16)
+        model.x.copy_(x)
+        model.capture()
+        model.prefill_standin(16)
+        outs.append(model.step().clone())
+        torch.cuda.synchronize()
+        assert model.routed.check_status()["code"] == 0
+        model.close()
+    # same random weights, e4m3 experts: the residual stream stays within a few percent
+    assert normwise_rel_err(outs[1], outs[0].float()) < 0.08

@@ -31,12 +31,12 @@ def _launch(n: int, script: str, *extra: str, timeout: int = 600) -> dict:
 
 
 def test_fused_layer_over_peer_memory_with_the_multi_cta_metadata_pass():
-    """Capacity 128 x top-8: 2048+ received slot words per rank, so the metadata pass runs as its two
+    """Capacity 1024 x top-8: more than 8192 received slot words per rank, so the metadata pass runs as its two
     chained multi-CTA launches behind real peers' dispatch flags."""
     n = min(torch.cuda.device_count(), 4)
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    out = _launch(n, "fixed_peer_check.py", "--dist", "uniform", "--iters", "4", "--replays", "20", "--capacity", "128",
+    out = _launch(n, "fixed_peer_check.py", "--dist", "uniform", "--iters", "4", "--replays", "20", "--capacity", "1024",
                   "--top-k", "8", "--experts", "64")
     assert out["ok"], out
 

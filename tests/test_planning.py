@@ -17,11 +17,12 @@ def test_tile_rows_follow_the_expected_rows_per_expert_not_the_worst_case():
 
 def test_metadata_ctas_by_size():
     assert choose_meta_ctas(8, 148) == 1
-    assert choose_meta_ctas(2047, 148) == 1
-    assert choose_meta_ctas(2048, 148) == 16
-    assert choose_meta_ctas(8192, 148) == 64
+    assert choose_meta_ctas(2048, 148) == 1
+    assert choose_meta_ctas(8192, 148) == 1       # EP=8, 128 tokens per rank, top-8: still the one-pass single CTA
+    assert choose_meta_ctas(8193, 148) == 65
+    assert choose_meta_ctas(16384, 148) == 128
     assert choose_meta_ctas(1 << 20, 148) == 148
-    assert choose_meta_ctas(4096, 8) == 8
+    assert choose_meta_ctas(16384, 8) == 8
 
 
 @pytest.fixture(scope="module")

@@ -415,3 +415,31 @@ def test_row_transport_round_trip_and_reentry_guard():
     torch.testing.assert_close(out, x * w.sum(dim=1, keepdim=True))
     with pytest.raises(RuntimeError, match="without a matching"):
         t.gather(out, torch.float32)
+
+
+def test_native_expert_kernels_are_chosen_by_weight_format():
+    """bf16 weights and block-scaled e4m3 weights (fp32 scale per 128x128 block) run on this framework's own
+    kernels; anything else keeps the engine's fused experts, or is an error when ``MOEFLOW_EXPERTS=native``."""
+    r = _FakeRunner(RunnerSettings.from_env({"MOEFLOW_MODE": "fixed"}), [1])
+    L, H, I = 2, 256, 128
+    layer = SimpleNamespace(backend="cuda", L=L, H=H, I=I)
+    bf16 = SimpleNamespace(w13_weight=torch.zeros(L, 2 * I, H, dtype=torch.bfloat16),
+                           w2_weight=torch.zeros(L, H, I, dtype=torch.bfloat16))
+    fp8 = SimpleNamespace(w13_weight=torch.zeros(L, 2 * I, H).to(torch.float8_e4m3fn),
+                          w2_weight=torch.zeros(L, H, I).to(torch.float8_e4m3fn),
+                          w13_weight_scale_inv=torch.ones(L, 2 * I // 128, H // 128),
+                          w2_weight_scale_inv=torch.ones(L, H // 128, I // 128))
+    per_tensor = SimpleNamespace(w13_weight=fp8.w13_weight, w2_weight=fp8.w2_weight,
+                                 w13_weight_scale=torch.ones(L), w2_weight_scale=torch.ones(L))
+    for experts, want in ((bf16, "bf16"), (fp8, "fp8"), (per_tensor, None)):
+        r.routed_experts = experts
+        assert r._use_native_experts(layer) == want
+    r.routed_experts = fp8
+    assert r._use_native_experts(SimpleNamespace(backend="torch", L=L, H=H, I=I)) is None
+    r.moeflow = replace(r.moeflow, experts="native")
+    r.routed_experts = per_tensor
+    with pytest.raises(ValueError):
+        r._use_native_experts(layer)
+    r.moeflow = replace(r.moeflow, experts="vllm")
+    r.routed_experts = bf16
+    assert r._use_native_experts(layer) is None
