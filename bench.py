@@ -16,7 +16,8 @@ point that fails is not timed (``oracle_err_max`` and ``status`` go into the JSO
 
 Timing protocol (both arms): W warm-up steps, then exactly K timed steps.  Before every step, outside
 the timed interval, the next input set of a rotating pool is copied into the static input buffers and
-a 256 MiB buffer is written to flush L2; ranks are aligned with a host barrier and then, on the device, by a
+a 256 MiB buffer is written to flush L2 (followed by a read pass over a second buffer, so that no dirty lines
+of the flush itself are written back during the step); ranks are aligned with a host barrier and then, on the device, by a
 one-element all-reduce enqueued on the launching stream right before the start event (so the ranks' streams
 enter the step together whatever the host-side jitter); the step is bracketed by CUDA events on the launching
 stream; the per-rank sum over the K steps is reduced with MAX over ranks, and the per-step times (MAX over
@@ -214,7 +215,11 @@ class OurArm:
         _lib.lib()  # the native library is mandatory here
         if DTYPE == "fp8":
             q13, s13, q2, s2 = w13  # block-scaled e4m3 pack (see make_local_weights_fp8); w2 is unused
-            self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, None, None, capacity=tokens, backend="cuda", device=dev)
+            from moeflow_b200.fixed import choose_block_m
+
+            rows = min(128, choose_block_m(tokens, TOP_K, EXPERTS // world))  # the fp8 kernels take tiles of up to 128 rows
+            self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, None, None, capacity=tokens, backend="cuda", device=dev,
+                                      gemm_kwargs={"block_m": rows})
             self.layer.set_weights_fp8(q13, s13, q2, s2)
         else:
             self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, w13, w2, capacity=tokens, backend="cuda")
@@ -357,7 +362,22 @@ def oracle_gate(out, x, logits, bias, expert_weights, rank, world, dev, n_check=
 # ------------------------------------------------------------------------------------------------
 # timing
 # ------------------------------------------------------------------------------------------------
-def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush: torch.Tensor, dev) -> list[float]:
+class L2Flusher:
+    """Writes a 256 MiB buffer (evicts everything), then reads a second one, so that the L2 is left holding clean
+    lines: the dirty lines of a bare memset would be written back during the first tens of microseconds of the
+    timed step and slow its cold loads down (both arms alike)."""
+
+    def __init__(self, dev, nbytes: int = 256 * 1024 * 1024):
+        self.dirty = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.clean = torch.zeros(nbytes // 4, dtype=torch.int32, device=dev)
+        self.sink = torch.zeros((), dtype=torch.int32, device=dev)
+
+    def zero_(self) -> None:
+        self.dirty.zero_()
+        torch.sum(self.clean, dim=0, dtype=torch.int32, out=self.sink)
+
+
+def timed_steps(step_fn, prepare_fn, steps: int, warmup: int, world: int, flush: "L2Flusher", dev) -> list[float]:
     """Device times of ``steps`` steps in ms (this rank).  prepare_fn(i) runs untimed."""
     align = torch.zeros(1, dtype=torch.float32, device=dev)
     for i in range(warmup):
@@ -485,7 +505,7 @@ def main() -> None:
             return w13_ref[e].float().cpu(), w2_ref[e].float().cpu()
 
     bias = (0.05 * torch.randn(EXPERTS, generator=torch.Generator().manual_seed(99))).to(dev)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    flush = L2Flusher(dev)
 
     sampler = ClockSampler(dev.index or 0)
     if rank == 0:
@@ -536,7 +556,7 @@ def main() -> None:
                 "seq_len": 1,
                 "parallelism": f"ep{world}",
                 "routing": args.dist,
-                "l2": "256 MiB buffer written before every timed step (L2 flush); local expert weights >> L2",
+                "l2": "before every timed step a 256 MiB buffer is written (L2 flush) and a second 256 MiB buffer is read (leaves clean lines, no pending write-back); local expert weights >> L2",
                 "timing": "per-step CUDA events; host barrier, then a one-element all-reduce on the stream before the start event (device-side alignment of the ranks); sum over steps, max over ranks",
                 "published_baseline_note": "published number is EP=4, intermediate 2048, real weights, L2-warm replays",
             },

@@ -23,7 +23,7 @@ from ..config import MoEConfig
 from ..ep_moe import EPMoELayer
 from ..fixed import FixedEPLayer
 
-BACKENDS = ("fused", "torch_fixed", "naive", "naive_tcgen05", "fixed_vllm_experts", "reference_fixed")
+BACKENDS = ("fused", "torch_fixed", "naive", "naive_tcgen05", "fixed_vllm_experts", "vllm_agrs", "reference_fixed")
 
 
 @dataclass
@@ -135,6 +135,68 @@ class FixedVllmExpertsBackend:
         return self.layer.forward_routed(x, w, ids, expert_fn=self._experts)[: x.shape[0]]
 
 
+class VllmNativeAgRsBackend:
+    """The serving engine's native expert-parallel data path, ``allgather_reducescatter``: every rank all-gathers
+    the hidden rows and routing of all ranks (NCCL), runs the engine's own fused experts on the gathered batch
+    with an expert map that keeps only its local experts, and a reduce-scatter (NCCL, bf16) returns to every rank
+    the sum of the ranks' partial outputs for its own tokens.
+
+    Assembled from vLLM's kernel object (``fused_experts`` with ``expert_map``) and ``torch.distributed``
+    collectives rather than through the engine's ``get_ep_group().dispatch``, which needs a fully initialised
+    engine (parallel state, forward context, workspace manager).  The steps and their order are those of the
+    engine's ``MoEPrepareAndFinalizeNaiveDPEPModular`` with the all-gather / reduce-scatter manager.  Same
+    router as the ``fused`` arm (the sm_100a router kernel), static buffers, CUDA-graph capturable.  Library
+    code on purpose: this is the comparison arm the routed layer has to beat.
+    Counterpart of ``VllmModularBackend("allgather_reducescatter")`` (``scripts/bench/backends.py:114-241``).
+    """
+
+    name = "vllm_agrs"
+
+    def __init__(self, cfg, info, w13_local, w2_local, bias, capacity, **_):
+        from vllm.model_executor.layers.fused_moe import fused_experts  # noqa: F401 - fails early without vLLM
+
+        self._fused_experts = fused_experts
+        self.cfg, self.bias, self.w13, self.w2, self.info = cfg, bias, w13_local, w2_local, info
+        dev, R, C, H, K, E = w13_local.device, info.world, capacity, cfg.hidden_size, cfg.top_k, cfg.n_routed_experts
+        L = cfg.experts_per_rank(R)
+        self.C = C
+        self.expert_map = torch.full((E,), -1, dtype=torch.int32, device=dev)
+        self.expert_map[info.rank * L:(info.rank + 1) * L] = torch.arange(L, dtype=torch.int32, device=dev)
+        self.x = torch.zeros(C, H, dtype=torch.bfloat16, device=dev)
+        self.w = torch.zeros(C, K, dtype=torch.float32, device=dev)
+        self.ids = torch.zeros(C, K, dtype=torch.int32, device=dev)
+        self.gx = torch.zeros(R * C, H, dtype=torch.bfloat16, device=dev)
+        self.gw = torch.zeros(R * C, K, dtype=torch.float32, device=dev)
+        self.gids = torch.zeros(R * C, K, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(C, H, dtype=torch.bfloat16, device=dev)
+
+    def run(self, x, logits):
+        from ..ops.kernels import router_topk
+
+        T = x.shape[0]
+        self.x[:T].copy_(x)
+        router_topk(logits, self.bias, self.cfg, self.w[:T], self.ids[:T])
+        if T < self.C:  # padding rows: weight 0 on a valid expert
+            self.w[T:].zero_()
+            self.ids[T:].zero_()
+        if self.info.world > 1:
+            dist.all_gather_into_tensor(self.gx, self.x)
+            dist.all_gather_into_tensor(self.gw, self.w)
+            dist.all_gather_into_tensor(self.gids, self.ids)
+        else:
+            self.gx.copy_(self.x)
+            self.gw.copy_(self.w)
+            self.gids.copy_(self.ids)
+        # the engine's SiLU-and-mul has no clamp; with a finite swiglu_limit the two arms differ where it bites
+        partial = self._fused_experts(self.gx, self.w13, self.w2, self.gw, self.gids,
+                                      global_num_experts=self.cfg.n_routed_experts, expert_map=self.expert_map)
+        if self.info.world > 1:
+            dist.reduce_scatter_tensor(self.out, partial.contiguous())
+        else:
+            self.out.copy_(partial)
+        return self.out[:T]
+
+
 class ReferenceFixedBackend:
     """The reference's own fixed layer with all four of its fusion switches (Triton + NCCL)."""
 
@@ -165,6 +227,7 @@ class ReferenceFixedBackend:
 def make_backend(name: str, *args, **kw):
     table = {"fused": FusedFixedBackend, "torch_fixed": TorchFixedBackend, "naive": NaiveBackend,
              "naive_tcgen05": NaiveTcgen05Backend, "fixed_vllm_experts": FixedVllmExpertsBackend,
+             "vllm_agrs": VllmNativeAgRsBackend,
              "reference_fixed": ReferenceFixedBackend}
     if name not in table:
         raise ValueError(f"unknown backend {name!r}; choose from {BACKENDS}")

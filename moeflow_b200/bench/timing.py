@@ -52,13 +52,22 @@ def aligned_start(group=None) -> None:
 
 
 class L2Flush:
-    """Overwrites a buffer larger than the 126 MB L2; whatever ran before is evicted."""
+    """Overwrites a buffer larger than the 126 MB L2, then reads a second one of the same size.
+
+    The write evicts whatever ran before.  It also leaves the L2 full of dirty lines, and their write-back would
+    compete with the first tens of microseconds of the timed work (measured on B200: cold loads at the start of a
+    layer took five times longer right after a plain memset); the read pass replaces them with clean lines, so the
+    timed region starts with a cold cache and an idle memory system.
+    """
 
     def __init__(self, nbytes: int = 256 << 20, device=None):
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device or "cuda")
+        self.clean = torch.zeros(nbytes // 4, dtype=torch.int32, device=device or "cuda")
+        self.sink = torch.zeros((), dtype=torch.int32, device=device or "cuda")
 
     def __call__(self) -> None:
         self.buf.zero_()
+        torch.sum(self.clean, dim=0, dtype=torch.int32, out=self.sink)
 
 
 class Stopwatch:

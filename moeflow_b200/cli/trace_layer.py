@@ -20,6 +20,7 @@ import dataclasses
 
 import torch
 
+from ..bench.timing import L2Flush
 from ..config import GLM53_FLASH_I1536
 from ..fixed import FixedEPLayer
 from ..testing import make_bias, make_hidden, make_logits
@@ -61,7 +62,7 @@ def main() -> None:
     layer._a_reduce.trace, layer._a_combine.trace = small["reduce+push"].data_ptr(), small["combine"].data_ptr()
     x = make_hidden(T, cfg, 3, device=dev)
     lg = make_logits(T, cfg, 4, device=dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = L2Flush(device=dev)  # write pass, then a read pass: cold cache, no write-back pending
     for _ in range(3):
         layer.forward(x, lg, bias)
     torch.cuda.synchronize()
@@ -69,7 +70,7 @@ def main() -> None:
     with torch.cuda.graph(graph):
         layer.forward(x, lg, bias)
     for _ in range(args.reps):
-        flush.zero_()
+        flush()
         for t in (tr_g1, tr_g2, *small.values()):
             t.zero_()
         torch.cuda.synchronize()

@@ -56,6 +56,20 @@ __device__ __forceinline__ uint32_t lane_id() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Warm-up touches.  A kernel launched with programmatic serialization sits idle until its predecessor is
+// done; the first access it then makes to every page costs an address-translation miss, and with a cold
+// L2 the page-table walk itself goes to DRAM (measured on B200: microseconds per first touch, one after
+// the other on a dependent chain).  touch() reads one word before the wait, so the translation is
+// in place and the line is in L2 when the real access comes.  The value read is never used (it may be stale).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void touch(const void* p) {
+  if (p == nullptr) return;
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  (void)v;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
 // may start while its predecessor in the stream is still running; it must call grid_dep_wait()
 // before it touches anything the predecessor writes (the wait returns when the predecessor has

@@ -288,16 +288,6 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_small_kernel(const m
   grid_dep_launch();
   for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
   if (tid == 0) warp_sums[34] = warp_sums[35] = 0;
-  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
-  if (trace) trace[1] = global_timer_ns();
-  const unsigned epoch = a.epoch ? *a.epoch : 0u;
-  if (a.flags != nullptr && tid < a.R) {
-    if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)(a.rows / a.R), a.wait_ns))
-      report_status(a.status, kDispatchFlagTimeout, tid, 0, epoch);
-  }
-  __syncthreads();
-  if (trace) trace[2] = global_timer_ns();  // flags seen
-
   const int N = a.rows * K;
   int per = (N + kMetaWarps - 1) / kMetaWarps;
   per = (per + 31) & ~31;               // <= 32 * kMetaBatch by the launcher's choice of this kernel
@@ -305,6 +295,38 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_small_kernel(const m
   const uint8_t* recv = static_cast<const uint8_t*>(a.recv);
   const size_t meta_off = (size_t)a.H * 2;
   int* my_hist = hist + warp * L;
+  {
+    // While the dispatch kernel runs: touch every page this kernel reads or writes after the wait.
+    if (tid == 0) {
+      touch(a.epoch);
+      touch(a.flags);
+      touch(a.plan);
+      touch(a.offsets);
+      touch(a.tile_e);
+      touch(a.tile_s);
+      touch(a.tile_n);
+      touch(a.row_hits);
+    }
+    const int i = begin + lane;
+    if (i < end) {
+      touch(recv + (size_t)(i / K) * a.pitch + meta_off);
+      touch(a.inv + i);
+      touch(a.entry_row + i);
+      touch(a.entry_slot + i);
+      touch(a.entry_w + i);
+    }
+    if (tid < a.n_counters1) touch(a.counters1 + tid);
+    if (tid < a.n_counters2) touch(a.counters2 + tid);
+  }
+  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
+  if (trace) trace[1] = global_timer_ns();
+  const unsigned epoch = a.epoch ? __ldcg(a.epoch) : 0u;
+  if (a.flags != nullptr && tid < a.R) {
+    if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)(a.rows / a.R), a.wait_ns))
+      report_status(a.status, kDispatchFlagTimeout, tid, 0, epoch);
+  }
+  __syncthreads();
+  if (trace) trace[2] = global_timer_ns();  // flags seen
 
   // the only reads of the received rows: id, valid flag and weight bits of every slot word of this thread
   int key[kMetaBatch], wbits[kMetaBatch], pre[kMetaBatch];

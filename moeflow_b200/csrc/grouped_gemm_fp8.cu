@@ -369,6 +369,52 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       }
 
       for (int j = 0; j < sg.nkb; ++j) {
+        if (!kGateUp && COLS == 32 && Cfg::kTmpStages >= 2 && j + 1 < sg.nkb) {
+          // Down projection, 32-column groups: two K blocks per round trip.  A K block is only 16 KB of weights
+          // here, so the fixed cost of a promotion step (barrier, tensor-memory load, fence, arrival) has to be
+          // shared between two of them to keep up with the weight stream.
+          F8Pipe nxt = tmp;
+          nxt.advance(Cfg::kTmpStages);
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_full[tmp.stage], tmp.phase, abort_flag, wait_ns));
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_full[nxt.stage], nxt.phase, abort_flag, wait_ns));
+          if (!ok) {
+            if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
+            break;
+          }
+          tc_fence_after_sync();
+          if (col0 < n_tile) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16) + col0;
+            uint32_t r0[32], r1[32];
+            tmem_ld_32(lane_base + tmp.stage * Cfg::kTmpCols, r0);
+            tmem_ld_32(lane_base + nxt.stage * Cfg::kTmpCols, r1);
+            tmem_ld_wait();
+            const float w0 = tblW[j], w1 = tblW[j + 1];
+            const float4* x0 = reinterpret_cast<const float4*>(tbl + j * N_MAX + col0);
+            const float4* x1 = reinterpret_cast<const float4*>(tbl + (j + 1) * N_MAX + col0);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 a0 = x0[q], a1 = x1[q];
+              acc_g[4 * q] = fmaf(__uint_as_float(r0[4 * q]), w0 * a0.x, acc_g[4 * q]);
+              acc_g[4 * q + 1] = fmaf(__uint_as_float(r0[4 * q + 1]), w0 * a0.y, acc_g[4 * q + 1]);
+              acc_g[4 * q + 2] = fmaf(__uint_as_float(r0[4 * q + 2]), w0 * a0.z, acc_g[4 * q + 2]);
+              acc_g[4 * q + 3] = fmaf(__uint_as_float(r0[4 * q + 3]), w0 * a0.w, acc_g[4 * q + 3]);
+              acc_g[4 * q] = fmaf(__uint_as_float(r1[4 * q]), w1 * a1.x, acc_g[4 * q]);
+              acc_g[4 * q + 1] = fmaf(__uint_as_float(r1[4 * q + 1]), w1 * a1.y, acc_g[4 * q + 1]);
+              acc_g[4 * q + 2] = fmaf(__uint_as_float(r1[4 * q + 2]), w1 * a1.z, acc_g[4 * q + 2]);
+              acc_g[4 * q + 3] = fmaf(__uint_as_float(r1[4 * q + 3]), w1 * a1.w, acc_g[4 * q + 3]);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&tmp_empty[tmp.stage]);
+            mbar_arrive(&tmp_empty[nxt.stage]);
+          }
+          tmp.advance(Cfg::kTmpStages);
+          tmp.advance(Cfg::kTmpStages);
+          ++j;
+          continue;
+        }
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&tmp_full[tmp.stage], tmp.phase, abort_flag, wait_ns));
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);

@@ -45,7 +45,7 @@ constexpr int kThreads = 256;
 constexpr int kThreadsWithReturn = 384;  // + 4 return warps (fused owner reduce + return push)
 constexpr int kRetDepth = 4;            // queued unit descriptors per quarter
 constexpr int kGatherThreads = 64;
-constexpr int kAccStages = 2;
+constexpr int kMaxAccStages = 2;
 constexpr int kMaxDevices = 64;        // devices one process may drive (per-device launch configuration)
 
 template <bool kGateUp, int N_MAX>
@@ -58,7 +58,10 @@ struct GemmCfg {
   // barriers): the bytes in flight per SM, not the tensor pipe, bound these weight-streaming kernels.
   static constexpr int kStages = (216 * 1024) / kStageBytes > 10 ? 10 : (216 * 1024) / kStageBytes;
   static constexpr int kAccCols = kATiles * N_MAX;
-  static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128}
+  // Two accumulator stages (the epilogue of unit i overlaps the main loop of unit i + 1) wherever the 512
+  // tensor-memory columns allow it; the gate/up GEMM with 256-row token tiles needs all 512 for one stage.
+  static constexpr int kAccStages = 2 * kAccCols <= 512 ? 2 : 1;
+  static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128, 256}
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/;
 };
 
@@ -179,9 +182,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
   uint64_t* full_bar = bars;                          // [STAGES]
   uint64_t* empty_bar = bars + STAGES;                // [STAGES]
-  uint64_t* acc_full = bars + 2 * STAGES;             // [kAccStages]
-  uint64_t* acc_empty = acc_full + kAccStages;        // [kAccStages]
-  uint64_t* ret_full = acc_empty + kAccStages;        // [4][kRetDepth] epilogue warp -> return warp
+  uint64_t* acc_full = bars + 2 * STAGES;             // [kMaxAccStages]
+  uint64_t* acc_empty = acc_full + kMaxAccStages;     // [kMaxAccStages]
+  uint64_t* ret_full = acc_empty + kMaxAccStages;        // [4][kRetDepth] epilogue warp -> return warp
   uint64_t* ret_empty = ret_full + 4 * kRetDepth;     // [4][kRetDepth]
   int* ret_desc = reinterpret_cast<int*>(ret_empty + 4 * kRetDepth);  // [4][kRetDepth][4]: n_rows, row_start, mb
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ret_desc + 4 * kRetDepth * 4);
@@ -206,7 +209,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       mbar_init(&full_bar[s], b_tma ? 2 : 1 + kGatherThreads);
       mbar_init(&empty_bar[s], 1);                  // tcgen05.commit
     }
-    for (int s = 0; s < kAccStages; ++s) {
+    for (int s = 0; s < Cfg::kAccStages; ++s) {
       mbar_init(&acc_full[s], 1);   // tcgen05.commit
       mbar_init(&acc_empty[s], 4);  // one per epilogue warp
     }
@@ -232,6 +235,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   // of the metadata kernel right away, so it waits first and only then lets the next kernel start:
   // when the down GEMM starts, the plan is therefore complete and it may stream weight tiles while
   // the gate/up GEMM is still finishing; only its token-operand producers wait for the activations.
+  if (tid < 8) {
+    // While the predecessor runs: touch the pages read right after the wait (see touch() in common.cuh).
+    const void* warm[8] = {a.plan, a.tile_e, a.tile_s, a.tile_n, a.b_index, a.row_scale, a.counters, a.tile_wait};
+    touch(warm[tid]);
+  }
   if (kGateUp) {
     grid_dep_wait();
     grid_dep_launch();
@@ -253,9 +261,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
   }
   // ---- the plan: tile count and the K cut, checked against what the caller's buffers can hold -----------
-  int n_tiles = a.plan[MF_PLAN_N_TILES];
-  const int cut = a.plan[a.split_word];  // 0 = stream-K, else the K split
-  int slot_cols = a.plan[MF_PLAN_SLOT_COLS];
+  int n_tiles = __ldcg(a.plan + MF_PLAN_N_TILES);
+  const int cut = __ldcg(a.plan + a.split_word);  // 0 = stream-K, else the K split
+  int slot_cols = __ldcg(a.plan + MF_PLAN_SLOT_COLS);
   if (slot_cols <= 0 || slot_cols > N_MAX) slot_cols = N_MAX;
   const long long slot_floats = (long long)Cfg::kATiles * slot_cols * kBlockM;
   const unsigned long long wait_ns = a.wait_ns;
@@ -354,7 +362,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if (!ok) break;
       if (lane == 0) umma_commit(&acc_full[acc.stage]);
       __syncwarp();
-      acc.advance(kAccStages);
+      acc.advance(Cfg::kAccStages);
     }
   } else if (warp < 4 && b_tma) {
     // ------------------------------------------------------------------ token-operand producer (TMA)
@@ -626,7 +634,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           if (with_return) ok = enqueue_return(n_rows, row_start, mb);
         }
       }
-      acc.advance(kAccStages);
+      acc.advance(Cfg::kAccStages);
       if (trace && warp == 4 && lane == 0) trace[5] = global_timer_ns();
     }
     if (it.bad_tile && warp == 4 && lane == 0) report_status(a.status, kBadArgument, 7, blockIdx.x, 0);
@@ -707,7 +715,7 @@ static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStre
 
 static int check_args(const mf_gemm_args* a, int n_max, int grid) {
   if (!a || grid < 1) return -1;
-  if (n_max != 32 && n_max != 64 && n_max != 128) return -2;
+  if (n_max != 32 && n_max != 64 && n_max != 128 && n_max != 256) return -2;
   if (a->m_blocks < 1 || a->k_blocks < 1) return -3;
   if ((a->b_pitch & 15) != 0 || (reinterpret_cast<uintptr_t>(a->b_base) & 15) != 0) return -4;
   if (a->b_tmap != nullptr && a->b_index != nullptr) return -5;  // TMA token tiles need contiguous rows
@@ -747,10 +755,12 @@ int mf_gemm_smem_bytes(int gate_up, int n_max) {
     if (n_max == 32) return mf::GemmCfg<true, 32>::kSmemBytes;
     if (n_max == 64) return mf::GemmCfg<true, 64>::kSmemBytes;
     if (n_max == 128) return mf::GemmCfg<true, 128>::kSmemBytes;
+    if (n_max == 256) return mf::GemmCfg<true, 256>::kSmemBytes;
   } else {
     if (n_max == 32) return mf::GemmCfg<false, 32>::kSmemBytes;
     if (n_max == 64) return mf::GemmCfg<false, 64>::kSmemBytes;
     if (n_max == 128) return mf::GemmCfg<false, 128>::kSmemBytes;
+    if (n_max == 256) return mf::GemmCfg<false, 256>::kSmemBytes;
   }
   return -1;
 }
@@ -761,7 +771,8 @@ int mf_gemm_gate_up(const void* tmap, const mf_gemm_args* args, int n_max, int g
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n_max == 32) return mf::launch<true, 32>(tmap, args, grid, s);
   if (n_max == 64) return mf::launch<true, 64>(tmap, args, grid, s);
-  return mf::launch<true, 128>(tmap, args, grid, s);
+  if (n_max == 128) return mf::launch<true, 128>(tmap, args, grid, s);
+  return mf::launch<true, 256>(tmap, args, grid, s);
 }
 
 int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid, mf_stream_t stream) {
@@ -771,11 +782,13 @@ int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid
   if (args->ret_peer != nullptr) {  // owner reduce + return push fused into the epilogue (four extra warps)
     if (n_max == 32) return mf::launch<false, 32, true>(tmap, args, grid, s);
     if (n_max == 64) return mf::launch<false, 64, true>(tmap, args, grid, s);
-    return mf::launch<false, 128, true>(tmap, args, grid, s);
+    if (n_max == 128) return mf::launch<false, 128, true>(tmap, args, grid, s);
+    return mf::launch<false, 256, true>(tmap, args, grid, s);
   }
   if (n_max == 32) return mf::launch<false, 32>(tmap, args, grid, s);
   if (n_max == 64) return mf::launch<false, 64>(tmap, args, grid, s);
-  return mf::launch<false, 128>(tmap, args, grid, s);
+  if (n_max == 128) return mf::launch<false, 128>(tmap, args, grid, s);
+  return mf::launch<false, 256>(tmap, args, grid, s);
 }
 
 }  // extern "C"

@@ -55,6 +55,13 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
                                                  (size_t)a.H * 2);
   const bool valid = __ldcg(meta + a.valid_word) != 0;
   if (valid && tid < a.K) s_pos[tid] = __ldcg(a.inv + (size_t)row * a.K + tid);
+  if (tid == 0) {
+    // touch the pages of the return path ahead of the wait: the pointer tables, this row's destination
+    touch(a.peer_ret + s);
+    touch(a.peer_flag + s);
+    touch(a.done_counter);
+    touch(a.push_epoch);
+  }
   grid_dep_wait();  // the down GEMM has completed: y is final
   if (trace) trace[1] = global_timer_ns();
   if (valid) {
@@ -111,10 +118,17 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
   unsigned long long* trace = (a.trace != nullptr && blockIdx.x == 0 && tid == 0) ? a.trace : nullptr;
   if (trace) trace[0] = global_timer_ns();
   if (tid == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.hit + (size_t)t * a.R));
+  // touch the pages read after the wait: flags, push count, this token's row in every owner's return block
+  if (tid < a.R) {
+    touch(a.flags != nullptr ? a.flags + tid : nullptr);
+    touch(static_cast<const uint8_t*>(a.ret) + ((size_t)tid * a.C + t) * a.H * 2);
+  }
+  if (tid == 32) touch(a.epoch);
+  if (tid == 33) touch(static_cast<const uint8_t*>(a.out) + (size_t)t * a.H * 2);
   grid_dep_wait();
   if (trace) trace[1] = global_timer_ns();
   if (tid < a.R) s_hit[tid] = __ldcg(a.hit + (size_t)t * a.R + tid);
-  const unsigned epoch = a.epoch ? *a.epoch : 0u;
+  const unsigned epoch = a.epoch ? __ldcg(a.epoch) : 0u;
   // counting flags: every owner adds one per received row of this rank (C of them) in every forward
   if (a.flags != nullptr && tid < a.R) {
     if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)a.C, a.wait_ns)) report_status(a.status, kReturnFlagTimeout, tid, t, epoch);

@@ -86,9 +86,9 @@ struct WorkIter {
       }
       s.tt = s.unit / m_blocks;
       s.mb = s.unit - s.tt * m_blocks;
-      s.e = a->tile_e[s.tt];
-      s.row_start = a->tile_s[s.tt];
-      s.n_rows = a->tile_n[s.tt];
+      s.e = __ldcg(a->tile_e + s.tt);
+      s.row_start = __ldcg(a->tile_s + s.tt);
+      s.n_rows = __ldcg(a->tile_n + s.tt);
       if ((unsigned)s.n_rows <= (unsigned)n_max) return true;
       bad_tile = true;  // a plan built for wider tiles than this kernel: skip the segment, every role alike
     }

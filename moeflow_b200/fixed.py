@@ -425,8 +425,8 @@ class FixedEPLayer:
         # routing (R*C*K entries over R*L experts), not the worst case: wide tiles cost pipeline stages, and
         # with few rows per expert the narrower tile keeps more weight bytes in flight.
         self.block_m = int(self.gemm_kwargs.get("block_m", choose_block_m(Cc, K, L)))
-        if self.block_m not in (32, 64, 128):
-            raise ValueError("block_m must be 32, 64 or 128")
+        if self.block_m not in (32, 64, 128, 256):
+            raise ValueError("block_m must be 32, 64, 128 or 256")
         self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
         self.max_tiles = (N + self.block_m - 1) // self.block_m + L
         self.out = torch.zeros(Cc, H, dtype=torch.bfloat16, device=dev)
@@ -538,7 +538,8 @@ class FixedEPLayer:
             self._a_gemm2.b_tmap = C.addressof(self._tmap_act)
         # Opt-in (gemm_kwargs permute_rows=True): copy the received hidden rows into expert-major order first,
         # so that the gate/up GEMM reads token tiles by TMA too instead of gathering them by entry index.
-        self.permute_rows = bool(self.gemm_kwargs.get("permute_rows", False))
+        # Default: on with 256-row tiles, where 64 gather threads would have to place 32 chunks each per stage.
+        self.permute_rows = bool(self.gemm_kwargs.get("permute_rows", self.block_m >= 256))
         if self.permute_rows:
             from .ops.kernels import make_tile_tmap
 
@@ -628,6 +629,8 @@ class FixedEPLayer:
             raise ValueError("scales must be one fp32 per 128x128 block")
         if H > 4096 or I > 4096:
             raise ValueError("fp8 path supports K <= 4096")
+        if self.block_m > 128:
+            raise ValueError("the fp8 kernels take token tiles of up to 128 rows: build the layer with gemm_kwargs={'block_m': 128}")
         pack = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
                 "s2": w2_s.to(torch.float32).contiguous()}
         pack["tm13"] = make_weight_tmap(pack["w13"].view(torch.uint8))
@@ -813,11 +816,14 @@ class _CudaLayout:
 
 
 def choose_block_m(capacity: int, top_k: int, local_experts: int) -> int:
-    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up (prefill).
+    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up, 256 from 512 up (long
+    prefill: a 256-row tile halves the operand bytes per flop that a CTA pulls from L2, which is what bounds the
+    compute-heavy regime).
 
     The expectation is the one under even routing: ``R * C * K`` entries over ``R * L`` experts.
     """
-    return 128 if (capacity * top_k) / max(local_experts, 1) >= 96 else 64
+    expected = (capacity * top_k) / max(local_experts, 1)
+    return 256 if expected >= 512 else 128 if expected >= 96 else 64
 
 
 def choose_meta_ctas(slot_words: int, n_sms: int) -> int:

@@ -483,6 +483,25 @@ def test_external_expert_function_on_the_cuda_backend(world, mode):
     assert bitwise_equal(got, combine_partials(cu[0].ret_recv, cu[0].hit, torch.bfloat16, 0, "bf16_ring"))
 
 
+def test_layer_with_256_row_tiles_matches_the_oracle():
+    """Long-prefill configuration: 256-row token tiles (one accumulator stage in the gate/up GEMM), received rows
+    copied into expert-major order and fetched by TMA, multi-CTA metadata pass; against the loop oracle."""
+    cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=4)
+    cap = 1100
+    w13, w2 = make_weights(cfg, 0, device="cuda")
+    bias = make_bias(cfg, 1, device="cuda")
+    xs, lgs = _inputs(cfg, 1, [cap - 5], 19)
+    ly = _layers(cfg, 1, cap, w13, w2, "cuda")[0]
+    assert ly.block_m == 256 and ly.permute_rows and ly.meta_ctas == 1
+    out = ly.forward(xs[0], lgs[0], bias).clone()
+    torch.cuda.synchronize()
+    _ok(ly)
+    n = 48
+    ref = moe_reference(xs[0][:n].cpu(), lgs[0][:n].cpu(), bias.cpu(), w13.cpu(), w2.cpu(), cfg)
+    assert normwise_rel_err(out[:n].cpu(), ref) < 4 * 2.0**-8
+    assert out[cap - 5:].abs().sum() == 0
+
+
 @pytest.mark.parametrize("world,cap,experts,top_k", [(1, 16, 16, 4), (2, 32, 16, 4), (1, 512, 16, 4)])
 def test_expert_major_copy_with_tma_token_tiles_equals_the_gather_bitwise(world, cap, experts, top_k):
     """gemm_kwargs permute_rows=True: received rows copied into expert-major order, gate/up token tiles by TMA.

@@ -60,6 +60,8 @@ CASES = [
     ([128], 256, 128, 128),  # one full 128-row tile: UMMA N = 128, both 128-column accumulators of a stage
     ([300, 5, 129], 512, 256, 128),  # experts spanning several 128-row tiles, a one-row remainder
     ([128, 128, 64], 256, 128, 128),
+    ([256], 256, 128, 256),  # 256-row tiles: UMMA N = 256, the gate/up accumulators fill all 512 tensor-memory columns
+    ([300, 5, 600], 512, 256, 256),
 ]
 
 
@@ -180,7 +182,8 @@ def test_down_proj_token_tiles_by_tma_equal_the_gather_bitwise(counts, block_m, 
 
 @pytest.mark.parametrize("counts,hidden,inter,block_m,split", [([3, 0, 17, 5], 512, 256, 64, 1), ([70, 2, 130], 512, 128, 64, 2),
                                                           ([128], 256, 128, 128, 1), ([300, 5, 129], 512, 256, 128, 1),
-                                                          ([127, 131, 3, 128], 256, 128, 128, 1), ([5, 9], 512, 256, 32, 4)])
+                                                          ([127, 131, 3, 128], 256, 128, 128, 1), ([5, 9], 512, 256, 32, 4),
+                                                          ([256, 700, 1], 512, 256, 256, 1), ([256], 256, 128, 256, 2)])
 def test_gate_up_token_tiles_by_tma_equal_the_gather_bitwise_and_the_oracle(counts, hidden, inter, block_m, split):
     """Gate/up GEMM with its token tiles fetched by TMA (contiguous rows) or gathered by cp.async: same bits,
     and both within tolerance of fp32 PyTorch.  Includes full 128-row tiles."""

@@ -87,5 +87,7 @@ def test_decode_model_with_fp8_experts_steps():
         torch.cuda.synchronize()
         assert model.routed.check_status()["code"] == 0
         model.close()
-    # same random weights, e4m3 experts: the residual stream stays within a few percent
-    assert normwise_rel_err(outs[1], outs[0].float()) < 0.08
+    # same random weights, e4m3 experts and activations: each MoE block is a few percent off and a token near a
+    # routing tie may change experts in the second layer, so the streams agree only roughly
+    assert torch.isfinite(outs[1].float()).all()
+    assert normwise_rel_err(outs[1], outs[0].float()) < 0.35

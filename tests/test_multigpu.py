@@ -63,3 +63,29 @@ def test_graph_gate_interleaved_capacities_shared_buffers_over_peers():
         pytest.skip("needs at least 2 GPUs")
     out = _launch(n, "fixed_graph_gate.py", "--replays", "1000", timeout=900)
     assert out["ok"] and out["replays"] == 1000, out
+
+
+def _launch_module(n: int, module: str, *extra: str, timeout: int = 900) -> str:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), "-m", module, *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert res.returncode == 0, f"rc={res.returncode}\n{res.stdout[-3000:]}\n{res.stderr[-3000:]}"
+    return res.stdout
+
+
+@pytest.mark.parametrize("arm_b", ["fused", "fixed_vllm_experts"])
+def test_native_allgather_reducescatter_arm_against_the_fixed_layer(arm_b, tmp_path):
+    """The paired native-vs-fixed driver end to end at a small shape: both arms pass the oracle gate on every rank,
+    each arm's graph replays equal its eager runs byte for byte, and a complete record is written."""
+    pytest.importorskip("vllm")
+    n = min(torch.cuda.device_count(), 2)
+    out = tmp_path / "ab.json"
+    text = _launch_module(n, "moeflow_b200.cli.ab_native_fixed", "--small", "--tokens", "1,8", "--reps", "3", "--inner", "5",
+                          "--check-graph-replays", "20", "--b", arm_b, "--out", str(out))
+    assert "T=8:" in text
+    record = json.loads(out.read_text())
+    points = record["results"]["points"]
+    assert [p["tokens"] for p in points] == [1, 8]
+    for p in points:
+        assert p["gate"]["a"]["passed"] and p["gate"]["b"]["passed"] and all(p["replays_ok"].values())
