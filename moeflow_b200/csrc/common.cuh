@@ -64,9 +64,13 @@ __device__ __forceinline__ uint32_t lane_id() {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void touch(const void* p) {
   if (p == nullptr) return;
-  unsigned v;
-  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  (void)v;
+  p = reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(3));  // a 4-byte load: align down (byte arrays)
+  asm volatile(
+      "{\n\t"
+      ".reg .u32 unused;\n\t"
+      "ld.volatile.global.u32 unused, [%0];\n\t"
+      "}" ::"l"(p)
+      : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -77,6 +81,16 @@ __device__ __forceinline__ void touch(const void* p) {
 // Both are no-ops in a kernel launched the ordinary way.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The whole CTA waits for the predecessor, but only one thread executes the wait instruction; the others sit
+// at the CTA barrier.  The wait makes the predecessor's writes visible to the grid, and the barrier orders the
+// other threads after it.  Measured on B200: with every thread of every early-resident CTA in
+// griddepcontrol.wait (148 GEMM CTAs of 256 threads, a thousand reduce CTAs), the kernels that were still
+// running took three times longer per phase; with one waiting thread per CTA they run at full speed.
+// All threads of the CTA must call this (it contains a __syncthreads()).
+__device__ __forceinline__ void grid_dep_wait_cta() {
+  if (threadIdx.x == 0) grid_dep_wait();
+  __syncthreads();
+}
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------

@@ -36,6 +36,20 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
   unsigned long long* trace = (a.trace != nullptr && blockIdx.x == 0 && tid == 0) ? a.trace : nullptr;
   if (trace) trace[0] = global_timer_ns();
   grid_dep_launch();  // the metadata kernel may get resident now; it waits for this grid to complete
+  {
+    // First touches in parallel instead of one after the other (see touch() in common.cuh): every page this CTA
+    // reads or writes, one lane each; warp 1 also touches this token's row in every destination's receive buffer.
+    if (tid < 12) {
+      const void* warm[12] = {a.epoch, a.num_valid, a.logits ? (const void*)(a.logits + (size_t)min(t, a.T > 0 ? a.T - 1 : 0) * a.E) : nullptr,
+                              a.bias, a.x, a.peer_recv, a.peer_flag, a.hit + (size_t)t * a.R, a.route_w, a.route_ids,
+                              a.done_counter, a.weights};
+      touch(warm[tid]);
+    } else if (tid >= 32 && tid < 32 + a.R && tid < 64) {
+      const int d = tid - 32;
+      touch(reinterpret_cast<const uint8_t*>(a.peer_recv[d]) + ((size_t)a.rank * a.C + t) * a.pitch);
+      touch(reinterpret_cast<const unsigned*>(a.peer_flag[d]) + a.rank);
+    }
+  }
   const unsigned epoch_next = *a.epoch + 1u;
   const bool has_token = t < a.T;
   const bool live = has_token && (a.num_valid == nullptr || t < *a.num_valid);

@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_kernel(const mf_meta
   if (trace) trace[0] = global_timer_ns();
   grid_dep_launch();
   for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
-  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
+  grid_dep_wait_cta();  // the dispatch kernel of this forward has completed (epoch, local rows)
   if (trace) trace[1] = global_timer_ns();
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
 
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_small_kernel(const m
     if (tid < a.n_counters1) touch(a.counters1 + tid);
     if (tid < a.n_counters2) touch(a.counters2 + tid);
   }
-  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
+  grid_dep_wait_cta();  // the dispatch kernel of this forward has completed (epoch, local rows)
   if (trace) trace[1] = global_timer_ns();
   const unsigned epoch = a.epoch ? __ldcg(a.epoch) : 0u;
   if (a.flags != nullptr && tid < a.R) {
@@ -557,7 +557,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_count_kernel(const m
   grid_dep_launch();
   for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
   if (tid == 0) warp_sums[0] = 0;
-  grid_dep_wait();  // the dispatch kernel of this forward has completed (epoch, local rows)
+  grid_dep_wait_cta();  // the dispatch kernel of this forward has completed (epoch, local rows)
   const unsigned epoch = a.epoch ? *a.epoch : 0u;
   if (a.flags != nullptr && tid < a.R) {
     if (!wait_flag_ge(a.flags + tid, epoch * (unsigned)(a.rows / a.R), a.wait_ns))
@@ -604,7 +604,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_place_kernel(const m
   grid_dep_launch();
   for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
   if (tid == 0) warp_sums[34] = 0;
-  grid_dep_wait();  // the count launch has completed (and with it the dispatch kernel)
+  grid_dep_wait_cta();  // the count launch has completed (and with it the dispatch kernel)
   __syncthreads();
 
   const int N = a.rows * K;

@@ -126,7 +126,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  grid_dep_wait();
+  grid_dep_wait_cta();
   grid_dep_launch();
 
   int n_tiles = a.plan[MF_PLAN_N_TILES];
@@ -577,7 +577,7 @@ quant_rows_kernel(const uint8_t* x, long long x_pitch, const int* row_index, int
   // Inputs are produced by kernels that may still run while this one is resident (programmatic launch), so
   // they are read from L2 (ld.global.cg), never through the non-coherent read-only path.
   grid_dep_launch();
-  grid_dep_wait();
+  grid_dep_wait_cta();
   const int r = blockIdx.x;
   if (n_rows_dev != nullptr && r >= __ldcg(n_rows_dev)) return;
   const long long src = row_index ? (long long)__ldcg(row_index + r) : (long long)r;

@@ -241,13 +241,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     touch(warm[tid]);
   }
   if (kGateUp) {
-    grid_dep_wait();
+    grid_dep_wait_cta();
     grid_dep_launch();
   } else {
     grid_dep_launch();
     // token-operand producers (act rows) and epilogue: after the whole gate/up grid, unless the activations
     // are handed over tile by tile (tile_wait), in which case nothing here depends on that grid's completion
-    if (warp >= 2 && a.tile_wait == nullptr) grid_dep_wait();
+    if (warp >= 2 && a.tile_wait == nullptr) {
+      if (lane == 0) grid_dep_wait();  // one waiting thread per warp (see grid_dep_wait_cta)
+      __syncwarp();
+    }
   }
 
   if (trace && tid == 0) trace[1] = global_timer_ns();

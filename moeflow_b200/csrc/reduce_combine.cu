@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
     touch(a.done_counter);
     touch(a.push_epoch);
   }
-  grid_dep_wait();  // the down GEMM has completed: y is final
+  grid_dep_wait_cta();  // the down GEMM has completed: y is final
   if (trace) trace[1] = global_timer_ns();
   if (valid) {
     __syncthreads();
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
   }
   if (tid == 32) touch(a.epoch);
   if (tid == 33) touch(static_cast<const uint8_t*>(a.out) + (size_t)t * a.H * 2);
-  grid_dep_wait();
+  grid_dep_wait_cta();
   if (trace) trace[1] = global_timer_ns();
   if (tid < a.R) s_hit[tid] = __ldcg(a.hit + (size_t)t * a.R + tid);
   const unsigned epoch = a.epoch ? __ldcg(a.epoch) : 0u;
@@ -217,7 +217,7 @@ expert_prepare_kernel(const uint8_t* rows, long long pitch, int H, int K, int ra
   // No __restrict__ / read-only loads here: this kernel may become resident (programmatic launch) before its
   // predecessors have written the rows, and loads through the non-coherent path are only defined for data that
   // does not change during the kernel's lifetime.  Every input produced earlier in the stream is read from L2.
-  grid_dep_wait();
+  grid_dep_wait_cta();
   const int r = blockIdx.x, tid = threadIdx.x;
   const uint8_t* row = rows + (size_t)r * pitch;
   const int* meta = reinterpret_cast<const int*>(row + (size_t)H * 2);
@@ -265,7 +265,7 @@ permute_rows_kernel(const uint8_t* recv, long long pitch, const int* entry_row, 
   // const __restrict__ data) is only defined for memory that does not change during the kernel's lifetime.
   // With such loads the copy returned rows of an earlier forward on the same addresses.
   grid_dep_launch();
-  grid_dep_wait();  // the metadata pass has completed: entry_row and the plan are final
+  grid_dep_wait_cta();  // the metadata pass has completed: entry_row and the plan are final
   const int n_entries = __ldcg(plan + MF_PLAN_N_ENTRIES);
   const int chunks = H / 8;
   for (int pos = blockIdx.x; pos < n_entries; pos += gridDim.x) {

@@ -69,6 +69,6 @@ def test_two_arm_serving_smoke_through_the_installed_engine(tmp_path):
             pytest.skip(f"{arm} arm: the engine did not finish within 300 s")
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     ours = json.loads(outs["moeflow"].read_text())
-    assert ours["runner_log"]["fixed_intercepted"] > 0 and ours["runner_log"]["experts"] == ["native"]
+    assert ours["runner_log"]["fixed_intercepted"] > 0 and ours["runner_log"]["experts"] == ["native-bf16"]
     verdict = smoke.compare(json.loads(outs["native"].read_text()), ours, 0.1, 0.05)
     assert verdict["passed"], verdict
