@@ -41,6 +41,7 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=288)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--fuse-return", type=int, default=0)
+    ap.add_argument("--gemm-kwargs", default="", help="extra FixedEPLayer gemm_kwargs as key=int pairs, comma separated")
     args = ap.parse_args()
     cfg = dataclasses.replace(GLM53_FLASH_I1536, n_routed_experts=args.experts)
     dev = torch.device("cuda")
@@ -52,7 +53,8 @@ def main() -> None:
         w13[e] = (torch.randn(2 * I, H, generator=g, device=dev) * (2.0 / H**0.5)).bfloat16()
         w2[e] = (torch.randn(H, I, generator=g, device=dev) / I**0.5).bfloat16()
     bias = make_bias(cfg, 1, device=dev)
-    layer = FixedEPLayer(cfg, 0, 1, w13, w2, capacity=T, backend="cuda", gemm_kwargs={"fuse_return": bool(args.fuse_return)})
+    extra = {k: int(v) for k, v in (kv.split("=") for kv in args.gemm_kwargs.split(",") if kv)}
+    layer = FixedEPLayer(cfg, 0, 1, w13, w2, capacity=T, backend="cuda", gemm_kwargs={"fuse_return": bool(args.fuse_return), **extra})
     n_sms = layer.n_sms
     tr_g1 = torch.zeros(n_sms, 8, dtype=torch.int64, device=dev)
     tr_g2 = torch.zeros_like(tr_g1)

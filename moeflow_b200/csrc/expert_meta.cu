@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(kMetaThreads) expert_meta_small_kernel(const m
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned long long* trace = (a.trace != nullptr && tid == 0) ? a.trace : nullptr;
   if (trace) trace[0] = global_timer_ns();
-  grid_dep_launch();
+  if (!a.late_launch) grid_dep_launch();
   for (int i = tid; i < kMetaWarps * L; i += kMetaThreads) hist[i] = 0;
   if (tid == 0) warp_sums[34] = warp_sums[35] = 0;
   const int N = a.rows * K;
@@ -729,7 +729,7 @@ extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
   if (a->n_ctas > 1) {
     if (!a->cta_hist || !a->acc || a->n_ctas > 1024) return -2;
     cudaError_t e = mf::launch_kernel(mf::expert_meta_count_kernel, dim3(a->n_ctas), dim3(mf::kMetaThreads), smem, s,
-                                      true, *a);
+                                      !a->plain_launch, *a);
     if (e != cudaSuccess) return (int)e;
     return (int)mf::launch_kernel(mf::expert_meta_place_kernel, dim3(a->n_ctas), dim3(mf::kMetaThreads), smem, s, true,
                                   *a);
@@ -737,6 +737,6 @@ extern "C" int mf_expert_meta(const mf_meta_args* a, mf_stream_t stream) {
   // one CTA: the register-resident one-pass kernel when every warp's range fits one batch of steps
   const long long n_words = (long long)a->rows * a->K;
   if (n_words <= (long long)mf::kMetaThreads * mf::kMetaBatch)
-    return (int)mf::launch_kernel(mf::expert_meta_small_kernel, dim3(1), dim3(mf::kMetaThreads), smem, s, true, *a);
-  return (int)mf::launch_kernel(mf::expert_meta_kernel, dim3(1), dim3(mf::kMetaThreads), smem, s, true, *a);
+    return (int)mf::launch_kernel(mf::expert_meta_small_kernel, dim3(1), dim3(mf::kMetaThreads), smem, s, !a->plain_launch, *a);
+  return (int)mf::launch_kernel(mf::expert_meta_kernel, dim3(1), dim3(mf::kMetaThreads), smem, s, !a->plain_launch, *a);
 }

@@ -9,6 +9,8 @@
 //              out[entry, mb*128 + r] = bf16( silu(min(gate, lim)) * clamp(up, +-lim) )
 //   down     : acc[128, n] = W2[e, mb*128 + r, :] . ACT[n, :]
 //              out[entry, mb*128 + r] = bf16( row_scale[entry] * acc )
+//              (two_blocks: a unit covers two adjacent weight blocks with two accumulators, like gate/up,
+//               so a token tile is fetched from L2 once per 256 output columns: the long-prefill form)
 //
 // A unit is (token tile, 128-row weight block); it needs k_blocks K steps.  The token tiles and the way
 // the units are cut along K come from a device-side plan (see expert_meta.cu), so nothing is read back
@@ -240,7 +242,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     const void* warm[8] = {a.plan, a.tile_e, a.tile_s, a.tile_n, a.b_index, a.row_scale, a.counters, a.tile_wait};
     touch(warm[tid]);
   }
-  if (kGateUp) {
+  if (kGateUp && !a.two_blocks) {
     grid_dep_wait_cta();
     grid_dep_launch();
   } else {
@@ -295,7 +297,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     WorkIter it = work;
     Seg sg;
     while (ok && it.next(sg)) {
-      const int row0 = sg.e * a.rows_per_expert + sg.mb * kBlockM;
+      const int row0 = sg.e * a.rows_per_expert + sg.mb * (a.two_blocks ? 2 * kBlockM : kBlockM);
       for (int j = 0; j < sg.nkb; ++j) {
         const int kb = sg.kb0 + j;
         ok = mbar_wait_bounded(&empty_bar[st.stage], st.phase ^ 1u, abort_flag, wait_ns);
@@ -521,7 +523,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16) + acc.stage * Cfg::kAccCols;
-      const long long out_col = (long long)mb * kBlockM + row;
+      const long long out_col = (long long)mb * (a.two_blocks ? 2 * kBlockM : kBlockM) + row;
       const bool col_ok = a.out_cols <= 0 || out_col < a.out_cols;  // weight rows padded up to a block are not stored
 
       if (sg.nseg == 1) {
@@ -535,7 +537,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             const int n = c0 + j;
             if (n < n_rows) {
               float v = __uint_as_float(g[j]);
-              if (kGateUp) {
+              if (kGateUp && a.two_blocks) {
+                // down projection over two adjacent weight blocks: two independent outputs, 128 columns apart
+                float w = __uint_as_float(up[j]);
+                if (a.row_scale) {
+                  const float sc = a.row_scale[row_start + n];
+                  v *= sc;
+                  w *= sc;
+                }
+                store_out(a, (long long)(row_start + n) * a.out_pitch + out_col + kBlockM, w);
+              } else if (kGateUp) {
                 float w = __uint_as_float(up[j]);
                 if (a.round_h) {
                   v = bf16_round(v);
@@ -614,7 +625,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
               const int n = n0 + j;
               if (n < n_rows) {
                 float r = v[j];
-                if (kGateUp) {
+                if (kGateUp && a.two_blocks) {
+                  float u = w[j];
+                  if (a.row_scale) {
+                    const float sc = a.row_scale[row_start + n];
+                    r *= sc;
+                    u *= sc;
+                  }
+                  store_out(a, (long long)(row_start + n) * a.out_pitch + out_col + kBlockM, u);
+                } else if (kGateUp) {
                   float u = w[j];
                   if (a.round_h) {
                     r = bf16_round(r);
@@ -782,6 +801,14 @@ int mf_gemm_down(const void* tmap, const mf_gemm_args* args, int n_max, int grid
   int c = mf::check_args(args, n_max, grid);
   if (c) return c;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (args->two_blocks) {
+    // two adjacent weight blocks per unit: the kernel form with two operand tiles and two accumulators
+    if (args->ret_peer != nullptr || args->out_cols > 0 || args->up_row_offset != mf::kBlockM) return -7;
+    if (n_max == 32) return mf::launch<true, 32>(tmap, args, grid, s);
+    if (n_max == 64) return mf::launch<true, 64>(tmap, args, grid, s);
+    if (n_max == 128) return mf::launch<true, 128>(tmap, args, grid, s);
+    return mf::launch<true, 256>(tmap, args, grid, s);
+  }
   if (args->ret_peer != nullptr) {  // owner reduce + return push fused into the epilogue (four extra warps)
     if (n_max == 32) return mf::launch<false, 32, true>(tmap, args, grid, s);
     if (n_max == 64) return mf::launch<false, 64, true>(tmap, args, grid, s);

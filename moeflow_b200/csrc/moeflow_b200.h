@@ -87,6 +87,9 @@ typedef struct {
   int* tile_done;
   const int* tile_wait;
   int tile_wait_target;
+  // mf_gemm_down only: 1 = a unit is two adjacent 128-row weight blocks (m_blocks counts pairs, up_row_offset
+  // must be 128): the token tile is shared by both, which halves its L2 traffic per output column.
+  int two_blocks;
 } mf_gemm_args;
 
 // Encode a 2-D tiled tensor map (K innermost) for a weight matrix [rows, k_elems]; box = 128 bytes x
@@ -208,6 +211,8 @@ typedef struct {
   // partial tiles per CTA; 0: always a K split from mf_plan_split.
   int stream_k;
   unsigned long long* trace; // optional [8] globaltimer stamps of CTA 0 (profiling aid), or NULL
+  int late_launch;           // 1: the kernels that follow may only start when this one exits (no early launch)
+  int plain_launch;          // 1: launched without programmatic serialization (starts when its predecessor has completed)
 } mf_meta_args;
 int mf_expert_meta(const mf_meta_args* args, mf_stream_t stream);
 // The K-split rule of the metadata kernels, callable on the host (no device needed): the split in {1,2,4,8}

@@ -486,6 +486,11 @@ class FixedEPLayer:
             k_blocks1=H // 64, m_blocks2=mb2, k_blocks2=I // 64, n_sms=self.n_sms,
             max_split_slots=self.max_split_slots, status=self.status.data_ptr(), wait_ns=self.wait_ns,
             partial_floats=partial_floats, stream_k=int(self.gemm_kwargs.get("stream_k", 0)),
+            # The metadata kernel is launched without programmatic serialization: started early, in the shadow of the
+            # dispatch kernel, its phases after the wait ran three times slower (measured on B200: 18 us against
+            # 8 us from dispatch end to plan), which cost more than the microsecond of launch latency it hid.  The
+            # GEMMs behind it still start early and overlap their prologues with it.
+            late_launch=int(self.gemm_kwargs.get("meta_late_launch", 0)), plain_launch=int(self.gemm_kwargs.get("meta_plain_launch", 1)),
         )
         # Metadata: one CTA for decode sizes; for prefill sizes (many received rows) the counting sort is
         # split over several CTAs in two chained launches.  Same result either way.
@@ -521,6 +526,13 @@ class FixedEPLayer:
             n_counters=self._counters2.numel(), **common,
         )
         self._a_gemm2.partial = self._partial[partial_floats:].data_ptr()
+        # Long prefill (256-row tiles): a down-projection unit covers two adjacent weight blocks, so a token tile is
+        # fetched from L2 once per 256 output columns (gemm_kwargs down_two_blocks overrides).
+        self.down_two_blocks = bool(self.gemm_kwargs.get("down_two_blocks", self.block_m >= 256)) and H % 256 == 0
+        if self.down_two_blocks:
+            g2 = self._a_gemm2
+            g2.two_blocks, g2.m_blocks, g2.up_row_offset = 1, H // 256, 128
+            self._a_meta.m_blocks2 = H // 256
         # Tile-level hand-over of the activations (gemm_kwargs tile_handover=False: the down GEMM waits for the
         # whole gate/up grid instead).
         self.tile_handover = bool(self.gemm_kwargs.get("tile_handover", True))

@@ -78,6 +78,7 @@ class GemmArgs(C.Structure):
         ("tile_done", C.c_void_p),
         ("tile_wait", C.c_void_p),
         ("tile_wait_target", C.c_int),
+        ("two_blocks", C.c_int),
     ]
 
 
@@ -156,6 +157,8 @@ class MetaArgs(C.Structure):
         ("acc", C.c_void_p),
         ("stream_k", C.c_int),
         ("trace", C.c_void_p),
+        ("late_launch", C.c_int),
+        ("plain_launch", C.c_int),
     ]
 
 

@@ -130,8 +130,11 @@ def down_proj(
     wait_ns: int = 2_000_000_000,
     grid: int | None = None,
     b_tma: bool = True,
+    two_blocks: bool = False,
 ) -> torch.Tensor:
     """``y[n] = bf16(row_scale[n] * (act[n] . W2[e_n]^T))`` per expert segment.
+
+    ``two_blocks``: a work unit covers two adjacent 128-row weight blocks (hidden must be a multiple of 256).
 
     ``b_tma``: fetch the token tiles of ``act`` by TMA (its rows are contiguous); ``False`` gathers them
     16 bytes at a time like the gate/up GEMM does for indexed rows.
@@ -150,10 +153,13 @@ def down_proj(
     grid = grid or sm_count(dev.index or 0)
     partial, counters, slots = _scratch(tp, hidden // 128, split, dev, grid)
     status = status if status is not None else torch.zeros(1, dtype=torch.int64, device=dev)
+    if two_blocks and hidden % 256:
+        raise ValueError("two_blocks needs a hidden size that is a multiple of 256")
     args = _lib.GemmArgs(
         b_base=act.data_ptr(), b_pitch=inter * 2, b_index=None, tile_e=tp.tile_e.data_ptr(), tile_s=tp.tile_s.data_ptr(),
-        tile_n=tp.tile_n.data_ptr(), plan=tp.plan.data_ptr(), split_word=_lib.PLAN_SPLIT2, m_blocks=hidden // 128,
-        k_blocks=inter // 64, rows_per_expert=hidden, up_row_offset=0, out=y.data_ptr(), out_pitch=hidden,
+        tile_n=tp.tile_n.data_ptr(), plan=tp.plan.data_ptr(), split_word=_lib.PLAN_SPLIT2,
+        m_blocks=hidden // 256 if two_blocks else hidden // 128, two_blocks=int(two_blocks),
+        k_blocks=inter // 64, rows_per_expert=hidden, up_row_offset=128 if two_blocks else 0, out=y.data_ptr(), out_pitch=hidden,
         row_scale=_lib.ptr(row_scale), partial=partial.data_ptr(), counters=counters.data_ptr(), max_split_slots=slots,
         limit=0.0, round_h=0, status=status.data_ptr(), wait_ns=wait_ns, partial_floats=partial.numel(),
         n_counters=counters.numel(), max_tiles=tp.tile_e.numel(),

@@ -241,3 +241,25 @@ def test_a_plan_that_does_not_fit_the_scratch_is_refused_on_the_device():
     st = decode_status(int(status.item()))
     assert st["code"] == 7, st
     assert float(y.float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("counts,hidden,inter,block_m,split", [([3, 0, 17, 5], 512, 256, 64, 1), ([70, 2, 130], 512, 128, 64, 2),
+                                                          ([128], 256, 128, 128, 1), ([256, 700, 1], 512, 256, 256, 1),
+                                                          ([300, 5, 600], 1024, 384, 256, 0)])
+def test_down_proj_over_two_weight_blocks_per_unit_equals_one_block_bitwise(counts, hidden, inter, block_m, split):
+    """``two_blocks``: a unit covers two adjacent 128-row weight blocks (two accumulators, the token tile fetched
+    once); every output element is the same dot product, so the bits equal the one-block kernel's."""
+    from moeflow_b200.ops.grouped_gemm import down_proj, plan_from_offsets
+
+    _, w2, _, _, offsets, scale = _problem(counts, hidden, inter, seed=41)
+    n = offsets[-1]
+    act = torch.randn(n, inter, generator=torch.Generator().manual_seed(4)).bfloat16().cuda()
+    tp = plan_from_offsets(offsets, block_m, act.device)
+    status = torch.zeros(1, dtype=torch.int64, device=act.device)
+    one = down_proj(act, w2, tp, row_scale=scale[:n], split=split, status=status, wait_ns=50_000_000).clone()
+    two = down_proj(act, w2, tp, row_scale=scale[:n], split=split, status=status, wait_ns=50_000_000, two_blocks=True).clone()
+    torch.cuda.synchronize()
+    _status_ok(status)
+    assert normwise_rel_err(two, _ref_down(act, w2, offsets, scale[:n])) < 4 * 2.0**-8
+    if split != 0:  # stream-K cuts units at different K positions in the two forms: equal values, other rounding
+        assert torch.equal(one.view(torch.int16), two.view(torch.int16))
