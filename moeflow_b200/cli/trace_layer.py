@@ -25,7 +25,8 @@ from ..config import GLM53_FLASH_I1536
 from ..fixed import FixedEPLayer
 from ..testing import make_bias, make_hidden, make_logits
 
-GEMM_EVENTS = ("entry", "deps met", "first weight tile", "first stage full", "first accumulator", "last epilogue", "exit")
+GEMM_EVENTS = ("entry", "deps met", "first weight tile", "first stage full", "first accumulator", "last epilogue", "exit",
+               "first epilogue done", "first chunk loaded", "first chunk stored", "first unit stored")
 SMALL_EVENTS = {
     "dispatch": ("entry", "routed", "rows stored", "fenced", "arrivals sent", "last CTA done"),
     "metadata": ("entry", "dispatch complete", "flags seen", "histogram", "plan written", "entries placed",
@@ -56,7 +57,7 @@ def main() -> None:
     extra = {k: int(v) for k, v in (kv.split("=") for kv in args.gemm_kwargs.split(",") if kv)}
     layer = FixedEPLayer(cfg, 0, 1, w13, w2, capacity=T, backend="cuda", gemm_kwargs={"fuse_return": bool(args.fuse_return), **extra})
     n_sms = layer.n_sms
-    tr_g1 = torch.zeros(n_sms, 8, dtype=torch.int64, device=dev)
+    tr_g1 = torch.zeros(n_sms, 16, dtype=torch.int64, device=dev)
     tr_g2 = torch.zeros_like(tr_g1)
     small = {name: torch.zeros(8, dtype=torch.int64, device=dev) for name in SMALL_EVENTS}
     layer._a_gemm1.trace, layer._a_gemm2.trace = tr_g1.data_ptr(), tr_g2.data_ptr()

@@ -315,8 +315,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           const bool live = n < s_.n_rows;
           long long idx = 0;
           if (live) idx = a.b_index ? (long long)a.b_index[s_.row_start + n] : (long long)(s_.row_start + n);
+          // all of the row's scales are requested before the first one is stored: one memory round trip per
+          // token instead of one per K block (a dependent load-store loop here cost as much as the unit's
+          // whole weight stream)
           const float* src = a.b_scale + idx * a.b_scale_pitch + s_.kb0;
-          for (int j = 0; j < s_.nkb; ++j) t[j * N_MAX + n] = live ? __ldcg(src + j) : 0.f;
+          float v[kF8MaxKb];
+#pragma unroll
+          for (int j = 0; j < kF8MaxKb; ++j) v[j] = (live && j < s_.nkb) ? __ldcg(src + j) : 0.f;
+#pragma unroll
+          for (int j = 0; j < kF8MaxKb; ++j)
+            if (j < s_.nkb) t[j * N_MAX + n] = v[j];
         }
       }
       if (pw < (kGateUp ? 2 : 1)) {
@@ -472,23 +480,29 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
       const long long out_col = (long long)mb * kF8BlockM + row;
       if (sg.nseg == 1) {
+        // 16 columns at a time: their arithmetic first (independent chains overlap), then their stores
+        __nv_bfloat16* p = out + (long long)(row_start + col0) * a.out_pitch + out_col;
+        const bool all = col0 + COLS <= n_rows;
 #pragma unroll
-        for (int c = 0; c < COLS; ++c) {
-          const int n = col0 + c;
-          if (n < n_rows) {
-            float v = acc_g[c];
-            if (kGateUp) {
-              float w = acc_u[c];
-              if (a.round_h) {
-                v = bf16_round(v);
-                w = bf16_round(w);
+        for (int c0 = 0; c0 < COLS; c0 += 16) {
+          if (kGateUp) {
+            if (a.round_h) {
+#pragma unroll
+              for (int c = c0; c < c0 + 16; ++c) {
+                acc_g[c] = bf16_round(acc_g[c]);
+                acc_u[c] = bf16_round(acc_u[c]);
               }
-              v = swiglu_clamped(v, w, a.limit);
-            } else if (a.row_scale) {
-              v *= a.row_scale[row_start + n];
             }
-            out[(long long)(row_start + n) * a.out_pitch + out_col] = __float2bfloat16_rn(v);
+#pragma unroll
+            for (int c = c0; c < c0 + 16; ++c) acc_g[c] = swiglu_clamped(acc_g[c], acc_u[c], a.limit);
+          } else if (a.row_scale) {
+#pragma unroll
+            for (int c = c0; c < c0 + 16; ++c)
+              acc_g[c] *= col0 + c < n_rows ? __ldcg(a.row_scale + row_start + col0 + c) : 1.f;
           }
+#pragma unroll
+          for (int c = c0; c < c0 + 16; ++c)
+            if (all || col0 + c < n_rows) p[(long long)c * a.out_pitch] = __float2bfloat16_rn(acc_g[c]);
         }
       } else {
         float* mine = a.partial + (long long)it.slot_of(sg, sg.seg) * slot_floats;

@@ -163,11 +163,53 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
 
 // One output element: bf16 (one rounding of the fp32 value), or fp32 as it is when the caller asked for it
 // (router logits from the down-projection kernel).
-__device__ __forceinline__ void store_out(const mf_gemm_args& a, long long index, float v) {
-  if (a.out_fp32)
-    static_cast<float*>(a.out)[index] = v;
-  else
-    static_cast<__nv_bfloat16*>(a.out)[index] = __float2bfloat16_rn(v);
+// Last step of the epilogue for C token columns of one weight row: the activation (gate/up), or the routing
+// weight (down), then the stores.  The arithmetic of all C columns comes first and has no branch that depends on
+// the column, so that the C dependency chains (exp, reciprocal) overlap: the epilogue warps are alone on their
+// scheduler and a column-by-column loop ran at one chain's latency (about 300 cycles per column).
+// v: first accumulator (gate, or the only one); w: second accumulator (up; with two_blocks the second weight block).
+template <bool kTwoAcc, int C>
+__device__ __forceinline__ void finish_store(const mf_gemm_args& a, float (&v)[C], float (&w)[C], const float (&sc)[C],
+                                             int n0, int n_rows, int row_start, long long out_col, bool col_ok) {
+  if (kTwoAcc && !a.two_blocks) {
+    if (a.round_h) {
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        v[j] = bf16_round(v[j]);
+        w[j] = bf16_round(w[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < C; ++j) v[j] = swiglu_clamped(v[j], w[j], a.limit);
+  } else if (a.row_scale) {
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      v[j] *= sc[j];
+      if (kTwoAcc) w[j] *= sc[j];
+    }
+  }
+  const bool second = kTwoAcc && a.two_blocks;  // the other weight block's outputs, 128 columns further
+  const bool all = n0 + C <= n_rows;
+  const long long first = (long long)(row_start + n0) * a.out_pitch + out_col;
+  if (a.out_fp32) {
+    float* p = static_cast<float*>(a.out) + first;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      if (all || n0 + j < n_rows) {
+        if (col_ok) p[(long long)j * a.out_pitch] = v[j];
+        if (second) p[(long long)j * a.out_pitch + kBlockM] = w[j];
+      }
+    }
+  } else {
+    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(a.out) + first;
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      if (all || n0 + j < n_rows) {
+        if (col_ok) p[(long long)j * a.out_pitch] = __float2bfloat16_rn(v[j]);
+        if (second) p[(long long)j * a.out_pitch + kBlockM] = __float2bfloat16_rn(w[j]);
+      }
+    }
+  }
 }
 
 template <bool kGateUp, int N_MAX, bool kReturn = false>
@@ -202,7 +244,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   const bool b_tma = a.b_tmap != nullptr;
   // Optional per-CTA time stamps: 0 entry, 1 dependencies met, 2 first weight tile requested, 3 first
   // operand stage complete, 4 first accumulator complete, 5 last epilogue done, 6 exit.
-  unsigned long long* trace = a.trace ? a.trace + (size_t)blockIdx.x * 8 : nullptr;
+  unsigned long long* trace = a.trace ? a.trace + (size_t)blockIdx.x * 16 : nullptr;
+  uint32_t stamped = 0;  // once-only stamps already written by this thread (a register, not a load of the trace word)
+  auto stamp_once = [&](int i) {
+    if (trace != nullptr && !(stamped & (1u << i))) {
+      stamped |= 1u << i;
+      trace[i] = global_timer_ns();
+    }
+  };
   if (trace && tid == 0) trace[0] = global_timer_ns();
 
   if (tid == 0) {
@@ -239,8 +288,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   // the gate/up GEMM is still finishing; only its token-operand producers wait for the activations.
   if (tid < 8) {
     // While the predecessor runs: touch the pages read right after the wait (see touch() in common.cuh).
-    const void* warm[8] = {a.plan, a.tile_e, a.tile_s, a.tile_n, a.b_index, a.row_scale, a.counters, a.tile_wait};
-    touch(warm[tid]);
+    const void* p = tid == 0 ? (const void*)a.plan : tid == 1 ? (const void*)a.tile_e : tid == 2 ? (const void*)a.tile_s
+                  : tid == 3 ? (const void*)a.tile_n : tid == 4 ? (const void*)a.b_index : tid == 5 ? (const void*)a.row_scale
+                  : tid == 6 ? (const void*)a.counters : (const void*)a.tile_wait;
+    touch(p);
   }
   if (kGateUp && !a.two_blocks) {
     grid_dep_wait_cta();
@@ -309,7 +360,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_bar[st.stage], Cfg::kStageA);
           uint8_t* dst = sA + st.stage * Cfg::kStageA;
-          if (trace && trace[2] == 0) trace[2] = global_timer_ns();
+          stamp_once(2);
           tma_load_2d(dst, &tmap_w, &full_bar[st.stage], kb * 64, row0);
           if (kGateUp) tma_load_2d(dst + kTileBytesA, &tmap_w, &full_bar[st.stage], kb * 64, row0 + a.up_row_offset);
         }
@@ -342,7 +393,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       for (int j = 0; j < sg.nkb; ++j) {
         ok = mbar_wait_bounded(&full_bar[st.stage], st.phase, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
-        if (trace && lane == 0 && trace[3] == 0) trace[3] = global_timer_ns();
+        if (lane == 0) stamp_once(3);
         if (!ok) {
           if (lane == 0) report_status(a.status, kGemmFullTimeout, 1, blockIdx.x, 0);
           break;
@@ -516,7 +567,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       if (n_tile < 16) n_tile = 16;
       ok = mbar_wait_bounded(&acc_full[acc.stage], acc.phase, abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
-      if (trace && warp == 4 && lane == 0 && trace[4] == 0) trace[4] = global_timer_ns();
+      if (warp == 4 && lane == 0) stamp_once(4);
       if (!ok) {
         if (lane == 0) report_status(a.status, kGemmAccTimeout, 3, blockIdx.x, 0);
         break;
@@ -526,40 +577,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const long long out_col = (long long)mb * (a.two_blocks ? 2 * kBlockM : kBlockM) + row;
       const bool col_ok = a.out_cols <= 0 || out_col < a.out_cols;  // weight rows padded up to a block are not stored
 
+      const bool scaled = a.row_scale != nullptr && (!kGateUp || a.two_blocks);
       if (sg.nseg == 1) {
+        // A real loop over 16-column groups (one copy of the code: unrolled over the whole tile it no longer fits
+        // the instruction cache, and every group is executed once per unit).  Lane l fetches the routing weight of
+        // column c0 + (l & 15) one group ahead.
+        auto scale_of = [&](int c0) {
+          const int n = c0 + (lane & 15);
+          return (scaled && n < n_rows) ? __ldcg(a.row_scale + row_start + n) : 1.f;
+        };
+        float s_next = scale_of(0);
+#pragma unroll 1
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           uint32_t g[16], up[16];
           tmem_ld_16(taddr + c0, g);
           if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
+          const float s_cur = s_next;
+          s_next = scale_of(c0 + 16);
           tmem_ld_wait();
+          if (warp == 4 && lane == 0) stamp_once(8);
+          float v[16], w[16], sc[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int n = c0 + j;
-            if (n < n_rows) {
-              float v = __uint_as_float(g[j]);
-              if (kGateUp && a.two_blocks) {
-                // down projection over two adjacent weight blocks: two independent outputs, 128 columns apart
-                float w = __uint_as_float(up[j]);
-                if (a.row_scale) {
-                  const float sc = a.row_scale[row_start + n];
-                  v *= sc;
-                  w *= sc;
-                }
-                store_out(a, (long long)(row_start + n) * a.out_pitch + out_col + kBlockM, w);
-              } else if (kGateUp) {
-                float w = __uint_as_float(up[j]);
-                if (a.round_h) {
-                  v = bf16_round(v);
-                  w = bf16_round(w);
-                }
-                v = swiglu_clamped(v, w, a.limit);
-              } else if (a.row_scale) {
-                v *= a.row_scale[row_start + n];
-              }
-              if (col_ok) store_out(a, (long long)(row_start + n) * a.out_pitch + out_col, v);
-            }
+            v[j] = __uint_as_float(g[j]);
+            w[j] = kGateUp ? __uint_as_float(up[j]) : 0.f;
+            sc[j] = scaled ? __shfl_sync(0xffffffffu, s_cur, j) : 1.f;
           }
+          finish_store<kGateUp, 16>(a, v, w, sc, c0, n_rows, row_start, out_col, col_ok);
+          if (warp == 4 && lane == 0) stamp_once(9);
         }
+        if (warp == 4 && lane == 0) stamp_once(10);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
@@ -620,32 +667,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 w[j] += pw[j];
               }
             }
+            float sc[kFix];
 #pragma unroll
-            for (int j = 0; j < kFix; ++j) {
-              const int n = n0 + j;
-              if (n < n_rows) {
-                float r = v[j];
-                if (kGateUp && a.two_blocks) {
-                  float u = w[j];
-                  if (a.row_scale) {
-                    const float sc = a.row_scale[row_start + n];
-                    r *= sc;
-                    u *= sc;
-                  }
-                  store_out(a, (long long)(row_start + n) * a.out_pitch + out_col + kBlockM, u);
-                } else if (kGateUp) {
-                  float u = w[j];
-                  if (a.round_h) {
-                    r = bf16_round(r);
-                    u = bf16_round(u);
-                  }
-                  r = swiglu_clamped(r, u, a.limit);
-                } else if (a.row_scale) {
-                  r *= a.row_scale[row_start + n];
-                }
-                if (col_ok) store_out(a, (long long)(row_start + n) * a.out_pitch + out_col, r);
-              }
-            }
+            for (int j = 0; j < kFix; ++j) sc[j] = (scaled && n0 + j < n_rows) ? __ldcg(a.row_scale + row_start + n0 + j) : 1.f;
+            finish_store<kGateUp, kFix>(a, v, w, sc, n0, n_rows, row_start, out_col, col_ok);
           }
           if (lane == 0) a.counters[sg.unit * 4 + wq] = 0;
           if (a.tile_done != nullptr) {
@@ -657,7 +682,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         }
       }
       acc.advance(Cfg::kAccStages);
-      if (trace && warp == 4 && lane == 0) trace[5] = global_timer_ns();
+      if (trace && warp == 4 && lane == 0) {
+        const unsigned long long now = global_timer_ns();
+        trace[5] = now;
+        if (!(stamped & (1u << 7))) {
+          stamped |= 1u << 7;
+          trace[7] = now;
+        }
+      }
     }
     if (it.bad_tile && warp == 4 && lane == 0) report_status(a.status, kBadArgument, 7, blockIdx.x, 0);
     if (with_return) enqueue_return(-1, 0, 0);  // tell the return warp that nothing more will come

@@ -51,7 +51,7 @@ typedef struct {
   const float* b_scale;      // [b rows, K/128] fp32 activation scales (1x128 groups)
   long long b_scale_pitch;   // floats between rows of b_scale
   float* out_scale;          // reserved
-  unsigned long long* trace; // optional [grid, 8] globaltimer stamps per CTA (profiling aid), or NULL
+  unsigned long long* trace; // optional [grid, 16] globaltimer stamps per CTA (profiling aid), or NULL
   // Down GEMM only, optional (ret_peer != NULL): owner reduce + return all-to-all fused into the epilogue.
   // When the last of a received row's slots has been written for a 32-column quarter of a block, that
   // warp sums the row's slots in slot order (fp32, from +0.0) and stores the bf16 partial straight into

@@ -239,8 +239,12 @@ class DecodeModel:
         self.routed = FixedEPLayer(cfg, rank, world, None, None, capacity=capacity, group=group, device=dev, backend="cuda")
         self.layers = []
         for layer in range(n_layers):
-            if weights_factory is not None:
-                w13, w2 = weights_factory(layer)
+            given = weights_factory(layer) if weights_factory is not None else None
+            prequantised = given is not None and len(given) == 4  # (w13_q, w13_s, w2_q, w2_s): e4m3 + block scales
+            if prequantised:
+                w13 = w2 = None
+            elif given is not None:
+                w13, w2 = given
             else:
                 w13 = torch.empty(L, 2 * I, H, dtype=torch.bfloat16, device=dev)
                 w2 = torch.empty(L, H, I, dtype=torch.bfloat16, device=dev)
@@ -248,7 +252,10 @@ class DecodeModel:
                     w13[e] = randn(2 * I, H, scale=2.0 / math.sqrt(H))
                     w2[e] = randn(H, I, scale=1.0 / math.sqrt(I))
             pack = None
-            if fp8:
+            if prequantised:
+                pack = self.routed.make_fp8_pack(*given)
+                maps = (None, None)
+            elif fp8:
                 from ..weights import quant_block_fp8
 
                 def quantise(w):
