@@ -48,6 +48,7 @@ constexpr int kThreadsWithReturn = 384;  // + 4 return warps (fused owner reduce
 constexpr int kRetDepth = 4;            // queued unit descriptors per quarter
 constexpr int kGatherThreads = 64;
 constexpr int kMaxAccStages = 2;
+constexpr int kOutStageBytes = 1024;   // 16 token columns x 32 weight rows of 16-bit outputs, per epilogue warp
 constexpr int kMaxDevices = 64;        // devices one process may drive (per-device launch configuration)
 
 template <bool kGateUp, int N_MAX>
@@ -64,7 +65,8 @@ struct GemmCfg {
   // tensor-memory columns allow it; the gate/up GEMM with 256-row token tiles needs all 512 for one stage.
   static constexpr int kAccStages = 2 * kAccCols <= 512 ? 2 : 1;
   static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128, 256}
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/ +
+                                    4 * kOutStageBytes /*one transposing store buffer per epilogue warp*/;
 };
 
 struct PipeState {
@@ -168,9 +170,13 @@ __device__ __forceinline__ void return_finish(const mf_gemm_args& a, int complet
 // the column, so that the C dependency chains (exp, reciprocal) overlap: the epilogue warps are alone on their
 // scheduler and a column-by-column loop ran at one chain's latency (about 300 cycles per column).
 // v: first accumulator (gate, or the only one); w: second accumulator (up; with two_blocks the second weight block).
+// With a staging buffer (`stage`, 1 KB of shared memory owned by the calling warp; C == 16; 16-bit outputs, all
+// columns stored) the 16 x 32 block is transposed through it, and every lane stores 16 bytes (8 weight rows of one
+// token): two store instructions per block instead of sixteen 64-byte ones.
 template <bool kTwoAcc, int C>
 __device__ __forceinline__ void finish_store(const mf_gemm_args& a, float (&v)[C], float (&w)[C], const float (&sc)[C],
-                                             int n0, int n_rows, int row_start, long long out_col, bool col_ok) {
+                                             int n0, int n_rows, int row_start, long long out_col, bool col_ok,
+                                             uint8_t* stage = nullptr, int lane = 0) {
   if (kTwoAcc && !a.two_blocks) {
     if (a.round_h) {
 #pragma unroll
@@ -189,6 +195,29 @@ __device__ __forceinline__ void finish_store(const mf_gemm_args& a, float (&v)[C
     }
   }
   const bool second = kTwoAcc && a.two_blocks;  // the other weight block's outputs, 128 columns further
+  if (C == 16 && stage != nullptr && !a.out_fp32 && a.out_cols <= 0 && (a.out_pitch & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.out) & 15) == 0) {  // 16-byte stores need rows that start on 16 bytes
+    __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out) + (long long)(row_start + n0) * a.out_pitch + (out_col - lane) +
+                         (lane & 3) * 8;
+    const uint4* src = reinterpret_cast<const uint4*>(stage) + lane;  // token lane / 4 (+ 8), rows 8 (lane & 3) ..
+#pragma unroll
+    for (int pass = 0; pass < (kTwoAcc ? 2 : 1); ++pass) {
+      if (pass == 1 && !second) break;
+      __syncwarp();  // the previous block's reads are done
+#pragma unroll
+      for (int j = 0; j < C; ++j) st[j * 32 + lane] = __float2bfloat16_rn(pass == 0 ? v[j] : w[j]);
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int t = 8 * h + (lane >> 2);
+        const uint4 x = src[32 * h];
+        if (n0 + t < n_rows)
+          *reinterpret_cast<uint4*>(out + (long long)t * a.out_pitch + (pass == 1 ? kBlockM : 0)) = x;
+      }
+    }
+    return;
+  }
   const bool all = n0 + C <= n_rows;
   const long long first = (long long)(row_start + n0) * a.out_pitch + out_col;
   if (a.out_fp32) {
@@ -233,6 +262,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   int* ret_desc = reinterpret_cast<int*>(ret_empty + 4 * kRetDepth);  // [4][kRetDepth][4]: n_rows, row_start, mb
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ret_desc + 4 * kRetDepth * 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* out_stage = smem + STAGES * Cfg::kStageBytes + 1024;  // [4 epilogue warps][kOutStageBytes]
   // The fused return path runs on four extra warps (the kernel is then launched with 384 threads).
   constexpr bool with_return = kReturn;  // the down GEMM with four extra warps for the fused return path
 
@@ -603,7 +633,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             w[j] = kGateUp ? __uint_as_float(up[j]) : 0.f;
             sc[j] = scaled ? __shfl_sync(0xffffffffu, s_cur, j) : 1.f;
           }
-          finish_store<kGateUp, 16>(a, v, w, sc, c0, n_rows, row_start, out_col, col_ok);
+          finish_store<kGateUp, 16>(a, v, w, sc, c0, n_rows, row_start, out_col, col_ok, out_stage + wq * kOutStageBytes, lane);
           if (warp == 4 && lane == 0) stamp_once(9);
         }
         if (warp == 4 && lane == 0) stamp_once(10);
