@@ -160,6 +160,7 @@ def make_local_weights(rank: int, world: int, dev: torch.device):
 
 ROUTING = "uniform"  # set from --dist
 DTYPE = "bf16"       # set from --dtype
+FP8_TILES = 256      # set from --fp8-tiles
 
 
 def make_local_weights_fp8(w13: torch.Tensor, w2: torch.Tensor):
@@ -217,10 +218,15 @@ class OurArm:
             q13, s13, q2, s2 = w13  # block-scaled e4m3 pack (see make_local_weights_fp8); w2 is unused
             from moeflow_b200.fixed import choose_block_m
 
-            rows = min(128, choose_block_m(tokens, TOP_K, EXPERTS // world))  # the fp8 kernels take tiles of up to 128 rows
+            # The e4m3 kernels take token tiles of up to 128 rows.  From 256-row tiles on (long prefill) the layer's
+            # default is to expand the e4m3 experts to bf16 inside every forward and run the bf16 kernels;
+            # --fp8-tiles 128 keeps the e4m3 tensor-core kernels there as well.
+            rows = min(FP8_TILES, choose_block_m(tokens, TOP_K, EXPERTS // world))
             self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, None, None, capacity=tokens, backend="cuda", device=dev,
                                       gemm_kwargs={"block_m": rows})
             self.layer.set_weights_fp8(q13, s13, q2, s2)
+            OurArm.fp8_path = ("e4m3 weights expanded to bf16 in every forward, bf16 tcgen05 GEMMs on 256-row tiles"
+                               if rows > 128 else "e4m3 tcgen05 GEMMs (kind::f8f6f4) with 1x128 e4m3 activations")
         else:
             self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, w13, w2, capacity=tokens, backend="cuda")
         self.g = GraphedMoELayer(self.layer, bias).capture()
@@ -470,12 +476,15 @@ def main() -> None:
     ap.add_argument("--dist", default="uniform", choices=["uniform", "zipf"], help="routing popularity profile")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
                     help="fp8: block-scaled e4m3 expert weights (128x128 blocks) and 1x128 e4m3 activations, bf16 in/out")
+    ap.add_argument("--fp8-tiles", type=int, default=256, choices=[128, 256],
+                    help="--dtype fp8: widest token tile; 256 lets long prefill expand the e4m3 experts to bf16 per forward")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    global ROUTING, DTYPE
+    global ROUTING, DTYPE, FP8_TILES
     ROUTING = args.dist
     DTYPE = args.dtype
+    FP8_TILES = args.fp8_tiles
 
     if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "moeflow" / "fixed.py").exists():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip --target install of the reference checkout)"}))
@@ -547,7 +556,8 @@ def main() -> None:
             "higher_is_better": False,
             "scaling": "weak",
             "vs_baseline": round(head["us_per_step"] / pub, 4) if pub else None,
-            "dtype": "bf16" if args.dtype == "bf16" else "fp8_e4m3 experts (128x128 weight blocks, 1x128 activation groups), bf16 in/out",
+            "dtype": "bf16" if args.dtype == "bf16" else "fp8_e4m3 experts (128x128 weight blocks), bf16 in/out: "
+                     + str(getattr(OurArm, "fp8_path", "")),
             "data": "synthetic tokens and uniform router logits, random-init weights N(0, 0.02-scale) of the named shape",
             "config": {
                 "model": "GLM-5.3-Flash routed MoE layer (hidden 4096, 288 experts, top-8, intermediate 1536)",

@@ -596,6 +596,7 @@ class FixedEPLayer:
         )
         self._tmap13 = self._tmap2 = None
         self._fp8 = None  # set by set_weights_fp8
+        self._expand = None  # e4m3 pack expanded to bf16 per forward (256-row token tiles)
         self._lib = _lib.lib()
         if self.w13 is not None:
             self.set_weights(self.w13, self.w2)
@@ -610,7 +611,7 @@ class FixedEPLayer:
         if w13_local.dtype != torch.bfloat16 or w2_local.dtype != torch.bfloat16:
             raise ValueError("cuda backend takes bf16 weights")
         self.w13, self.w2 = w13_local.contiguous(), w2_local.contiguous()
-        self._fp8 = None
+        self._fp8 = self._expand = None
         self._tmap13 = make_weight_tmap(self.w13)
         self._tmap2 = make_weight_tmap(self.w2)
 
@@ -641,13 +642,31 @@ class FixedEPLayer:
             raise ValueError("scales must be one fp32 per 128x128 block")
         if H > 4096 or I > 4096:
             raise ValueError("fp8 path supports K <= 4096")
-        if self.block_m > 128:
-            raise ValueError("the fp8 kernels take token tiles of up to 128 rows: build the layer with gemm_kwargs={'block_m': 128}")
         pack = {"w13": w13_q.contiguous(), "w2": w2_q.contiguous(), "s13": w13_s.to(torch.float32).contiguous(),
                 "s2": w2_s.to(torch.float32).contiguous()}
+        if self.block_m > 128:
+            # Long-prefill layers (256-row token tiles): the block-scaled kernels take tiles of up to 128 rows and are
+            # bound by their per-K-block promotion there, so every forward expands the bound experts into a bf16
+            # scratch (shared by all layers of this shape on the device) and runs the bf16 kernels on it.
+            pack["expand"] = True
+            return pack
         pack["tm13"] = make_weight_tmap(pack["w13"].view(torch.uint8))
         pack["tm2"] = make_weight_tmap(pack["w2"].view(torch.uint8))
         return pack
+
+    _expand_scratch: dict = {}  # (device index, L, I, H) -> bf16 weight scratch + tensor maps, shared between layers
+
+    def _expanded_weights(self) -> dict:
+        from .ops.kernels import make_weight_tmap
+
+        key = (self.device.index, self.L, self.I, self.H)
+        e = FixedEPLayer._expand_scratch.get(key)
+        if e is None:
+            w13 = torch.empty(self.L, 2 * self.I, self.H, dtype=torch.bfloat16, device=self.device)
+            w2 = torch.empty(self.L, self.H, self.I, dtype=torch.bfloat16, device=self.device)
+            e = {"w13": w13, "w2": w2, "tm13": make_weight_tmap(w13), "tm2": make_weight_tmap(w2)}
+            FixedEPLayer._expand_scratch[key] = e
+        return e
 
     def _fp8_buffers(self) -> dict:
         """Quantised activations and the fp8 GEMM argument blocks of this buffer set (allocated on first use)."""
@@ -686,6 +705,12 @@ class FixedEPLayer:
 
     def bind_weights_fp8(self, pack: dict) -> None:
         """Point this (possibly shared) buffer set at one MoE layer's e4m3 weights; no copies."""
+        if pack.get("expand"):
+            e = self._expanded_weights()
+            self._fp8, self._expand = None, pack
+            self.w13, self.w2, self._tmap13, self._tmap2 = e["w13"], e["w2"], e["tm13"], e["tm2"]
+            return
+        self._expand = None
         f = self._fp8_buffers()
         f["a1"].w_scale, f["a2"].w_scale = pack["s13"].data_ptr(), pack["s2"].data_ptr()
         f["tm13"], f["tm2"], f["pack"] = pack["tm13"], pack["tm2"], pack
@@ -709,7 +734,7 @@ class FixedEPLayer:
         if tmap13 is None or tmap2 is None:
             self.set_weights(w13_local, w2_local)
             return
-        self._fp8 = None
+        self._fp8 = self._expand = None
         self.w13, self.w2, self._tmap13, self._tmap2 = w13_local, w2_local, tmap13, tmap2
 
     def _cuda_dispatch(self, x, weights, ids, num_valid, logits=None, bias=None) -> torch.Tensor:
@@ -750,6 +775,13 @@ class FixedEPLayer:
         if self._tmap13 is None:
             raise RuntimeError("no expert weights bound (set_weights)")
         s = _lib.stream_ptr()
+        if self._expand is not None:
+            # before the metadata kernel: the expansion depends on nothing of this forward and overlaps the dispatch
+            p, lib = self._expand, self._lib
+            _lib.check(lib.mf_dequant_block_fp8(p["w13"].data_ptr(), p["s13"].data_ptr(), self.w13.data_ptr(),
+                                                self.L * 2 * self.I, self.H, s), "expand e4m3 gate/up weights")
+            _lib.check(lib.mf_dequant_block_fp8(p["w2"].data_ptr(), p["s2"].data_ptr(), self.w2.data_ptr(),
+                                                self.L * self.H, self.I, s), "expand e4m3 down weights")
         self._cuda_meta()
         if stop_after == "META":
             return

@@ -233,6 +233,7 @@ def lib() -> C.CDLL:
         "mf_gemm_gate_up_fp8": [P, C.POINTER(GemmArgs), I, I, P],
         "mf_gemm_down_fp8": [P, C.POINTER(GemmArgs), I, I, P],
         "mf_quant_rows_1x128": [P, LL, P, I, I, P, P, LL, P, P],
+        "mf_dequant_block_fp8": [P, P, P, LL, I, P],
         "mf_router_topk": [P, P, P, P, I, I, I, I, I, I, I, F, P],
         "mf_rmsnorm": [P, P, P, I, I, F, P],
         "mf_dispatch_push": [C.POINTER(DispatchArgs), P],

@@ -116,3 +116,27 @@ def down_proj_fp8(aq, a_s, w2_q, w2_s, tp: TilePlan, row_scale=None, split=1, st
     y = torch.zeros(max(tp.n_entries, 1), hidden, dtype=torch.bfloat16, device=aq.device)
     return _gemm_fp8(False, aq, a_s, w2_q, w2_s, tp, y, None, row_scale, None, split, status, wait_ns, grid,
                      b_tma=b_tma)[: tp.n_entries]
+
+
+def expand_block_fp8(w_q: torch.Tensor, w_s: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Block-scaled e4m3 weights ``[..., rows, K]`` with fp32 scales ``[..., rows/128, K/128]`` -> bf16, one pass.
+
+    ``out`` (bf16, same shape, contiguous) is overwritten when given.  Used by layers that hold e4m3 experts and run
+    the bf16 grouped GEMMs on long-prefill tiles.
+    """
+    if w_q.dtype not in (torch.float8_e4m3fn, torch.uint8) or not w_q.is_contiguous():
+        raise ValueError("contiguous e4m3 weights expected")
+    K = w_q.shape[-1]
+    rows = w_q.numel() // K
+    if rows % 128 or K % 128:
+        raise ValueError("rows and K must be multiples of 128")
+    w_s = w_s.to(torch.float32).contiguous()
+    if w_s.numel() != (rows // 128) * (K // 128):
+        raise ValueError("one fp32 scale per 128x128 block expected")
+    if out is None:
+        out = torch.empty(w_q.shape, dtype=torch.bfloat16, device=w_q.device)
+    elif out.dtype != torch.bfloat16 or out.numel() != w_q.numel() or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 tensor of the weights' shape")
+    _lib.check(_lib.lib().mf_dequant_block_fp8(w_q.data_ptr(), w_s.data_ptr(), out.data_ptr(), rows, K, _lib.stream_ptr()),
+               "expand e4m3 weights")
+    return out

@@ -162,3 +162,55 @@ def test_layer_with_fp8_weights_matches_dequantised_oracle(world):
         # activations are e4m3 (3 mantissa bits) per 128-wide group: a few percent is the format, not a bug
         assert err < 0.06, err
         assert outs[r][t:].abs().sum() == 0
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (3, 256, 512), (2, 384, 1536)])
+def test_expand_block_fp8_equals_definition(shape):
+    """e4m3 x block scale -> bf16 in one pass equals the PyTorch dequantisation rounded once to bf16."""
+    from moeflow_b200.ops.fp8 import expand_block_fp8
+
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(*shape, generator=g) * 0.05
+    flat = w.reshape(-1, shape[-2], shape[-1])
+    qs, ss = zip(*(quant_block_fp8(m) for m in flat))
+    q = torch.stack([t.view(torch.uint8) for t in qs]).view(torch.float8_e4m3fn).reshape(shape).cuda()
+    s = torch.stack(list(ss)).cuda()
+    out = expand_block_fp8(q, s)
+    torch.cuda.synchronize()
+    ref = torch.stack([dequant_block_fp8(a, b) for a, b in zip(qs, ss)]).reshape(shape).to(torch.bfloat16)
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_layer_expands_fp8_weights_on_256_row_tiles():
+    """A layer built with 256-row token tiles and e4m3 weights expands them to bf16 in every forward and then equals,
+    bit for bit, the same layer bound to the dequantised bf16 weights."""
+    from moeflow_b200 import MoEConfig
+    from moeflow_b200.fixed import FixedEPLayer, simulate_fixed
+    from moeflow_b200.parallel.peer import PeerGroup
+    from moeflow_b200.testing import make_bias, make_hidden, make_logits, make_weights
+
+    cfg = MoEConfig(hidden_size=512, moe_intermediate_size=256, n_routed_experts=4, top_k=2)
+    cap = 600
+    w13, w2 = make_weights(cfg, 0, dtype=torch.float32)
+    packs = [(quant_block_fp8(w13[e]), quant_block_fp8(w2[e])) for e in range(cfg.n_routed_experts)]
+    w13_dq = torch.stack([dequant_block_fp8(*p[0]) for p in packs]).to(torch.bfloat16).cuda()
+    w2_dq = torch.stack([dequant_block_fp8(*p[1]) for p in packs]).to(torch.bfloat16).cuda()
+    bias = make_bias(cfg, 1, device="cuda")
+    stack8 = lambda ts: torch.stack([t.view(torch.uint8) for t in ts]).view(torch.float8_e4m3fn).cuda()  # noqa: E731
+    outs = []
+    for fp8 in (True, False):
+        region = PeerGroup.local(1, FixedEPLayer.peer_bytes(cfg, 1, cap))[0]
+        ly = FixedEPLayer(cfg, 0, 1, None if fp8 else w13_dq, None if fp8 else w2_dq, capacity=cap, backend="cuda",
+                          device="cuda", peer_region=region, wait_ns=50_000_000, gemm_kwargs={"block_m": 256})
+        if fp8:
+            ly.set_weights_fp8(stack8([p[0][0] for p in packs]), torch.stack([p[0][1] for p in packs]).cuda(),
+                               stack8([p[1][0] for p in packs]), torch.stack([p[1][1] for p in packs]).cuda())
+        x = make_hidden(cap, cfg, 30, device="cuda")
+        lg = make_logits(cap, cfg, 40, device="cuda")
+        for _ in range(2):  # the second forward re-expands into the same scratch
+            out = simulate_fixed([ly], [x], [lg], bias)[0].clone()
+        torch.cuda.synchronize()
+        assert ly.check_status()["code"] == 0
+        outs.append(out)
+    assert torch.isfinite(outs[0].float()).all() and outs[0].abs().sum() > 0
+    assert torch.equal(outs[0], outs[1])
