@@ -45,6 +45,11 @@ constexpr int kBlockM = 128;          // weight rows per block (UMMA M)
 constexpr int kTileBytesA = 128 * 128;  // 128 rows x 128 bytes
 constexpr int kThreads = 256;
 constexpr int kThreadsWithReturn = 384;  // + 4 return warps (fused owner reduce + return push)
+// Epilogue warp groups.  Tiles of 256 token columns fill all 512 tensor-memory columns with one accumulator stage
+// (two accumulators of 256 columns), so their epilogue is not hidden behind the next unit's main loop: two groups of
+// four warps then take half of the token columns each.  The variant with return warps keeps one group.
+template <int N_MAX, bool kReturn>
+constexpr int kEpiGroups = (N_MAX >= 256 && !kReturn) ? 2 : 1;
 constexpr int kRetDepth = 4;            // queued unit descriptors per quarter
 constexpr int kGatherThreads = 64;
 constexpr int kMaxAccStages = 2;
@@ -66,7 +71,7 @@ struct GemmCfg {
   static constexpr int kAccStages = 2 * kAccCols <= 512 ? 2 : 1;
   static constexpr int kTmemCols = kAccStages * kAccCols;  // power of two for N_MAX in {32, 64, 128, 256}
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 1024 /*barriers, return queue*/ +
-                                    4 * kOutStageBytes /*one transposing store buffer per epilogue warp*/;
+                                    (N_MAX >= 256 ? 8 : 4) * kOutStageBytes /*one transposing store buffer per epilogue warp*/;
 };
 
 struct PipeState {
@@ -242,11 +247,12 @@ __device__ __forceinline__ void finish_store(const mf_gemm_args& a, float (&v)[C
 }
 
 template <bool kGateUp, int N_MAX, bool kReturn = false>
-__global__ void __launch_bounds__(kReturn ? kThreadsWithReturn : kThreads, 1)
+__global__ void __launch_bounds__(kReturn ? kThreadsWithReturn : 128 + 128 * kEpiGroups<N_MAX, kReturn>, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_b,
                     const mf_gemm_args a) {
   using Cfg = GemmCfg<kGateUp, N_MAX>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr int kGroups = kEpiGroups<N_MAX, kReturn>;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -292,7 +298,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
     for (int s = 0; s < Cfg::kAccStages; ++s) {
       mbar_init(&acc_full[s], 1);   // tcgen05.commit
-      mbar_init(&acc_empty[s], 4);  // one per epilogue warp
+      mbar_init(&acc_empty[s], 4 * kGroups);  // one per epilogue warp
     }
     for (int s = 0; s < 4 * kRetDepth; ++s) {
       mbar_init(&ret_full[s], 1);
@@ -362,7 +368,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     bool bad = n_tiles < 0 || !(cut == 0 || cut == 1 || cut == 2 || cut == 4 || cut == 8) ||
                (cut > 1 && a.k_blocks % cut != 0);
     bad = bad || (a.max_tiles > 0 && n_tiles > a.max_tiles);
-    bad = bad || (a.n_counters > 0 && (long long)n_tiles * a.m_blocks * 4 > (long long)a.n_counters);
+    bad = bad || (a.n_counters > 0 && (long long)n_tiles * a.m_blocks * 4 * kGroups > (long long)a.n_counters);
     bad = bad || (a.partial_floats > 0 && work.slots_needed() * slot_floats > a.partial_floats);
     if (bad) {
       if (tid == 0) report_status(a.status, kBadArgument, 6, blockIdx.x, 0);
@@ -561,9 +567,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
     // Drain this thread's cp.async operations before the CTA may exit.
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp < 8) {
+  } else if (warp < 4 + 4 * kGroups) {
     // ------------------------------------------------------------------ epilogue
     const int wq = warp & 3;                 // TMEM lane quarter this warp may read
+    const int grp = (warp - 4) >> 2;         // column group (0 unless kGroups == 2)
     const int row = wq * 32 + lane;          // weight row inside the block
     PipeState acc;
     PipeState rq;                            // position in this quarter's return queue
@@ -608,6 +615,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const bool col_ok = a.out_cols <= 0 || out_col < a.out_cols;  // weight rows padded up to a block are not stored
 
       const bool scaled = a.row_scale != nullptr && (!kGateUp || a.two_blocks);
+      // this warp group's share of the token columns (whole 16-column groups)
+      const int c_half = kGroups == 2 ? ((n_tile / 16 + 1) / 2) * 16 : n_tile;
+      const int c_begin = grp * c_half;
+      const int c_end = (kGroups == 2 && grp == 0) ? c_half : n_tile;
+      const int counter_ix = (sg.unit * 4 + wq) * kGroups + grp;
       if (sg.nseg == 1) {
         // A real loop over 16-column groups (one copy of the code: unrolled over the whole tile it no longer fits
         // the instruction cache, and every group is executed once per unit).  Lane l fetches the routing weight of
@@ -616,9 +628,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const int n = c0 + (lane & 15);
           return (scaled && n < n_rows) ? __ldcg(a.row_scale + row_start + n) : 1.f;
         };
-        float s_next = scale_of(0);
+        float s_next = scale_of(c_begin);
 #pragma unroll 1
-        for (int c0 = 0; c0 < n_tile; c0 += 16) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
           uint32_t g[16], up[16];
           tmem_ld_16(taddr + c0, g);
           if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
@@ -633,7 +645,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             w[j] = kGateUp ? __uint_as_float(up[j]) : 0.f;
             sc[j] = scaled ? __shfl_sync(0xffffffffu, s_cur, j) : 1.f;
           }
-          finish_store<kGateUp, 16>(a, v, w, sc, c0, n_rows, row_start, out_col, col_ok, out_stage + wq * kOutStageBytes, lane);
+          finish_store<kGateUp, 16>(a, v, w, sc, c0, n_rows, row_start, out_col, col_ok, out_stage + (warp - 4) * kOutStageBytes, lane);
           if (warp == 4 && lane == 0) stamp_once(9);
         }
         if (warp == 4 && lane == 0) stamp_once(10);
@@ -650,7 +662,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         // The unit is cut along K: park the fp32 partial sums, then the last quarter-warp to arrive adds
         // the segments in K order.
         float* mine = a.partial + (long long)it.slot_of(sg, sg.seg) * slot_floats;
-        for (int c0 = 0; c0 < n_tile; c0 += 16) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
           uint32_t g[16], up[16];
           tmem_ld_16(taddr + c0, g);
           if (kGateUp) tmem_ld_16(taddr + N_MAX + c0, up);
@@ -670,7 +682,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         __threadfence();
         __syncwarp();
         int old = 0;
-        if (lane == 0) old = atomicAdd(&a.counters[sg.unit * 4 + wq], 1);
+        if (lane == 0) old = atomicAdd(&a.counters[counter_ix], 1);
         old = __shfl_sync(0xffffffffu, old, 0);
         if (old == sg.nseg - 1) {
           __threadfence();
@@ -678,7 +690,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           // took one column per L2 round trip cost tens of microseconds on 64-column tiles); the sums
           // still run over the segments in K order for every column.
           constexpr int kFix = 8;
-          for (int n0 = 0; n0 < n_rows; n0 += kFix) {
+          const int n_stop = n_rows < c_end ? n_rows : c_end;  // this group's columns that hold rows
+          for (int n0 = c_begin; n0 < n_stop; n0 += kFix) {
             float v[kFix], w[kFix];
 #pragma unroll
             for (int j = 0; j < kFix; ++j) v[j] = w[j] = 0.f;
@@ -702,7 +715,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             for (int j = 0; j < kFix; ++j) sc[j] = (scaled && n0 + j < n_rows) ? __ldcg(a.row_scale + row_start + n0 + j) : 1.f;
             finish_store<kGateUp, kFix>(a, v, w, sc, n0, n_rows, row_start, out_col, col_ok);
           }
-          if (lane == 0) a.counters[sg.unit * 4 + wq] = 0;
+          if (lane == 0) a.counters[counter_ix] = 0;
           if (a.tile_done != nullptr) {
             __threadfence();
             __syncwarp();
@@ -793,7 +806,7 @@ static int launch(const void* tmap, const mf_gemm_args* args, int grid, cudaStre
   CUtensorMap tm, tb;
   memcpy(&tm, tmap, sizeof(tm));
   memcpy(&tb, args->b_tmap ? args->b_tmap : tmap, sizeof(tb));
-  const int threads = kReturn ? kThreadsWithReturn : kThreads;
+  const int threads = kReturn ? kThreadsWithReturn : 128 + 128 * kEpiGroups<N_MAX, kReturn>;
   return (int)launch_kernel(kern, dim3(grid), dim3(threads), Cfg::kSmemBytes, stream, true, tm, tb, *args);
 }
 

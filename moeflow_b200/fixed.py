@@ -539,7 +539,8 @@ class FixedEPLayer:
         if self.tile_handover:
             self._a_gemm1.tile_done = self._tile_done.data_ptr()
             self._a_gemm2.tile_wait = self._tile_done.data_ptr()
-            self._a_gemm2.tile_wait_target = 4 * mb1
+            # one count per epilogue warp of the gate/up GEMM and weight block: two groups of four at 256-row tiles
+            self._a_gemm2.tile_wait_target = (8 if self.block_m >= 256 else 4) * mb1
         # The down GEMM reads its token operand (act, contiguous in expert-major order) by TMA, one bulk copy
         # per pipeline stage; gemm_kwargs b_tma=False falls back to the 16-byte gather the gate/up GEMM uses.
         self._tmap_act = None
@@ -776,7 +777,7 @@ class FixedEPLayer:
             raise RuntimeError("no expert weights bound (set_weights)")
         s = _lib.stream_ptr()
         if self._expand is not None:
-            # before the metadata kernel: the expansion depends on nothing of this forward and overlaps the dispatch
+            # before the metadata kernel: the expansion depends on nothing of this forward
             p, lib = self._expand, self._lib
             _lib.check(lib.mf_dequant_block_fp8(p["w13"].data_ptr(), p["s13"].data_ptr(), self.w13.data_ptr(),
                                                 self.L * 2 * self.I, self.H, s), "expand e4m3 gate/up weights")
