@@ -47,7 +47,7 @@ def main() -> None:
     ap.add_argument("--small", action="store_true", help="small layer shape (smoke runs)")
     ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (keeps hidden/intermediate)")
     ap.add_argument("--only-full", action="store_true", help="time only the whole layer (profiling runs)")
-    ap.add_argument("--block-m", type=int, default=None, help="token rows per GEMM tile (32, 64, 128); default: chosen by the layer")
+    ap.add_argument("--block-m", type=int, default=None, help="token rows per GEMM tile (32, 64, 128, 256); default: chosen by the layer")
     ap.add_argument("--meta-ctas", type=int, default=None, help="CTAs of the metadata pass (1 = single-CTA kernel); default: by size")
     ap.add_argument("--permute-rows", action="store_true",
                     help="copy received rows into expert-major order so the gate/up GEMM reads token tiles by TMA")

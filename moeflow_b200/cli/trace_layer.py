@@ -2,9 +2,10 @@
 
     python -m moeflow_b200.cli.trace_layer --tokens 128 --experts 36
 
-Every kernel of the forward takes an optional trace buffer: the two grouped GEMMs stamp seven events per CTA
+Every kernel of the forward takes an optional trace buffer: the two grouped GEMMs stamp eleven events per CTA
 (entry, dependencies met, first weight tile requested, first operand stage complete, first accumulator
-complete, last epilogue done, exit), the transport kernels stamp CTA 0 (dispatch: entry, routed, rows stored,
+complete, last epilogue done, exit, and for the first unit: epilogue done, first 16-column group loaded from
+tensor memory, first group stored, all groups stored), the transport kernels stamp CTA 0 (dispatch: entry, routed, rows stored,
 fenced, arrivals sent, last CTA done; metadata: entry, dispatch complete, flags seen, histogram, plan written,
 entries placed; reduce + push: entry, GEMM complete, row stored, fenced, -, last CTA done; combine: entry,
 predecessor complete, return flags seen, row written).  The layer is captured in a CUDA graph, replayed with a
