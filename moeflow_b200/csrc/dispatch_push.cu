@@ -22,10 +22,13 @@
 
 namespace mf {
 
-constexpr int kDispatchThreads = 256;
+// Threads per CTA: 256 at decode sizes (the hidden row is loaded and stored by many lanes at once); 128 from 1024
+// token positions on, where the kernel is bound by how many CTAs (one token each: a routing warp and its latency)
+// an SM holds at a time, and half-size CTAs double that number.
 constexpr int kMaxTopK = 32;
 constexpr int kMaxRanks = 256;
 
+template <int kDispatchThreads>
 __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const mf_dispatch_args a) {
   __shared__ int s_id[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
@@ -149,8 +152,9 @@ __global__ void __launch_bounds__(kDispatchThreads) dispatch_push_kernel(const m
 }  // namespace mf
 
 extern "C" int mf_dispatch_push(const mf_dispatch_args* a, mf_stream_t stream) {
+  const int threads = (a && a->C >= 1024 && a->H / 8 <= 128 * 4 && a->R <= 32) ? 128 : 256;
   if (!a || a->C < 1 || a->T > a->C || a->K > mf::kMaxTopK || a->R > mf::kMaxRanks || a->H % 8 != 0 ||
-      a->H / 8 > mf::kDispatchThreads * 4 || (a->pitch & 15) != 0 || a->pitch < (long long)a->H * 2 + (2 * a->K + 1) * 4)
+      a->H / 8 > threads * 4 || (a->pitch & 15) != 0 || a->pitch < (long long)a->H * 2 + (2 * a->K + 1) * 4)
     return -1;
   size_t smem = 0;
   if (a->logits != nullptr) {
@@ -158,6 +162,9 @@ extern "C" int mf_dispatch_push(const mf_dispatch_args* a, mf_stream_t stream) {
     smem = 2 * (size_t)a->E * sizeof(float);
     if (smem > 40 * 1024) return -3;
   }
-  mf::dispatch_push_kernel<<<a->C, mf::kDispatchThreads, smem, static_cast<cudaStream_t>(stream)>>>(*a);
+  if (threads == 128)
+    mf::dispatch_push_kernel<128><<<a->C, 128, smem, static_cast<cudaStream_t>(stream)>>>(*a);
+  else
+    mf::dispatch_push_kernel<256><<<a->C, 256, smem, static_cast<cudaStream_t>(stream)>>>(*a);
   return (int)cudaGetLastError();
 }

@@ -109,7 +109,9 @@ __global__ void __launch_bounds__(kRowThreads) owner_reduce_push_kernel(const mf
   }
 }
 
-__global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_args a) {
+// kThreads: kRowThreads at decode sizes, 128 from 1024 token positions on (one CTA per token: more CTAs per SM).
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) combine_kernel(const mf_combine_args a) {
   __shared__ unsigned char s_hit[256];
   const int t = blockIdx.x;
   const int tid = threadIdx.x;
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(kRowThreads) combine_kernel(const mf_combine_a
   const uint4* ret = static_cast<const uint4*>(a.ret);
   uint4* out = static_cast<uint4*>(a.out) + (size_t)t * chunks;
   const unsigned char* hit = s_hit;
-  for (int c = tid; c < chunks; c += kRowThreads) {
+  for (int c = tid; c < chunks; c += kThreads) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (!a.ring) {
       for (int d0 = 0; d0 < a.R; d0 += 8) {
@@ -190,7 +192,10 @@ int mf_owner_reduce_push(const mf_reduce_push_args* a, mf_stream_t stream) {
 
 int mf_combine(const mf_combine_args* a, mf_stream_t stream) {
   if (!a || a->H % 8 != 0 || a->R < 1 || a->R > mf::kRowThreads || a->C < 1) return -1;
-  return (int)mf::launch_kernel(mf::combine_kernel, dim3(a->C), dim3(mf::kRowThreads), 0,
+  if (a->C >= 1024 && a->R <= 32)
+    return (int)mf::launch_kernel(mf::combine_kernel<128>, dim3(a->C), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                                  true, *a);
+  return (int)mf::launch_kernel(mf::combine_kernel<mf::kRowThreads>, dim3(a->C), dim3(mf::kRowThreads), 0,
                                 static_cast<cudaStream_t>(stream), true, *a);
 }
 

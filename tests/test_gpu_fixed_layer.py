@@ -44,9 +44,9 @@ def _ok(layer):
 
 @pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("dist", ["uniform", "hotspot"])
-def test_dispatch_rows_bitwise_equal_torch_twin(world, dist):
+@pytest.mark.parametrize("cap", [16, 1100])  # 1100: the half-size CTAs the kernel uses from 1024 token positions on
+def test_dispatch_rows_bitwise_equal_torch_twin(world, dist, cap):
     cfg = SMALL_GPU
-    cap = 16
     w13, w2 = make_weights(cfg, 0, device="cuda")
     bias = make_bias(cfg, 1, device="cuda")
     tokens = [cap, 5, 0, 11][:world]
@@ -220,9 +220,10 @@ def test_layer_matches_oracle_and_twin(world, dist):
         assert err < gemm_tolerance(err_twin), (err, err_twin)
 
 
-def test_owner_reduce_and_combine_bitwise_given_same_y():
+@pytest.mark.parametrize("cap", [8, 1100])  # 1100: the combine kernel's half-size CTAs
+def test_owner_reduce_and_combine_bitwise_given_same_y(cap):
     """With the same expert outputs y, return rows and the combined output equal the torch twin bitwise."""
-    world, cap = 2, 8
+    world = 2
     cfg = replace(SMALL_GPU, n_routed_experts=8, top_k=4)
     w13, w2 = make_weights(cfg, 0, device="cuda")
     xs, lgs = _inputs(cfg, world, [cap, 5], 5)
