@@ -861,14 +861,15 @@ class _CudaLayout:
 
 
 def choose_block_m(capacity: int, top_k: int, local_experts: int) -> int:
-    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up, 256 from 512 up (long
+    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up, 256 from 384 up (long
     prefill: a 256-row tile halves the operand bytes per flop that a CTA pulls from L2, which is what bounds the
-    compute-heavy regime).
+    compute-heavy regime).  384 is where the measured rates of the two tile widths (849 and 1158 TFLOP/s for the
+    gate/up GEMM) times the fill of the last tile break even.
 
     The expectation is the one under even routing: ``R * C * K`` entries over ``R * L`` experts.
     """
     expected = (capacity * top_k) / max(local_experts, 1)
-    return 256 if expected >= 512 else 128 if expected >= 96 else 64
+    return 256 if expected >= 384 else 128 if expected >= 96 else 64
 
 
 def choose_meta_ctas(slot_words: int, n_sms: int) -> int:

@@ -12,6 +12,8 @@ def test_tile_rows_follow_the_expected_rows_per_expert_not_the_worst_case():
     assert choose_block_m(128, 8, 36) == 64      # EP=8, T=128: 28 rows per expert (worst case would be 227)
     assert choose_block_m(2048, 8, 144) == 128   # EP=2 prefill: 114 rows per expert
     assert choose_block_m(8192, 8, 36) == 256    # EP=8 long prefill: 1820 rows per expert
+    assert choose_block_m(8192, 8, 144) == 256   # EP=2 long prefill: 455 rows per expert
+    assert choose_block_m(4096, 8, 144) == 128   # 228 rows per expert
     assert choose_block_m(512, 8, 144) == 64
     assert choose_block_m(1, 8, 1) == 64
 
