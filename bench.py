@@ -221,7 +221,7 @@ class OurArm:
             # The e4m3 kernels take token tiles of up to 128 rows.  From 256-row tiles on (long prefill) the layer's
             # default is to expand the e4m3 experts to bf16 inside every forward and run the bf16 kernels;
             # --fp8-tiles 128 keeps the e4m3 tensor-core kernels there as well.
-            rows = min(FP8_TILES, choose_block_m(tokens, TOP_K, EXPERTS // world))
+            rows = min(FP8_TILES, choose_block_m(tokens, TOP_K, EXPERTS // world, fp8=True))
             self.layer = FixedEPLayer(GLM53_FLASH_I1536, rank, world, None, None, capacity=tokens, backend="cuda", device=dev,
                                       gemm_kwargs={"block_m": rows})
             self.layer.set_weights_fp8(q13, s13, q2, s2)

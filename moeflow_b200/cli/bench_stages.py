@@ -87,6 +87,7 @@ def main() -> None:
     for T in [int(t) for t in args.tokens.split(",")]:
         layer = FixedEPLayer(cfg, info.rank, info.world, w13, w2, capacity=T, backend=args.backend,
                              gemm_kwargs={**({"block_m": args.block_m} if args.block_m else {}),
+                                          **({"fp8_weights": True} if args.fp8 else {}),
                                           **({"meta_ctas": args.meta_ctas} if args.meta_ctas else {}),
                                           **({"permute_rows": True} if args.permute_rows else {}),
                                           **({"stream_k": args.stream_k} if args.stream_k is not None else {}),

@@ -424,7 +424,10 @@ class FixedEPLayer:
         # number of times an expert's weights are streamed.  The estimate is the expectation under even
         # routing (R*C*K entries over R*L experts), not the worst case: wide tiles cost pipeline stages, and
         # with few rows per expert the narrower tile keeps more weight bytes in flight.
-        self.block_m = int(self.gemm_kwargs.get("block_m", choose_block_m(Cc, K, L)))
+        # A buffer set built without weights may be bound to e4m3 experts later: plan its tiles for them unless told
+        # otherwise (gemm_kwargs fp8_weights=False / True).
+        fp8_hint = bool(self.gemm_kwargs.get("fp8_weights", self.w13 is None))
+        self.block_m = int(self.gemm_kwargs.get("block_m", choose_block_m(Cc, K, L, fp8=fp8_hint)))
         if self.block_m not in (32, 64, 128, 256):
             raise ValueError("block_m must be 32, 64, 128 or 256")
         self.n_sms = int(self.gemm_kwargs.get("n_sms", sm_count(dev.index if dev.index is not None else 0)))
@@ -860,16 +863,23 @@ class _CudaLayout:
         self.total = self.rflag_off + up(world * 4, 256)
 
 
-def choose_block_m(capacity: int, top_k: int, local_experts: int) -> int:
-    """Token rows per GEMM tile: 64 for decode, 128 from 96 expected rows per expert up, 256 from 384 up (long
-    prefill: a 256-row tile halves the operand bytes per flop that a CTA pulls from L2, which is what bounds the
-    compute-heavy regime).  384 is where the measured rates of the two tile widths (849 and 1158 TFLOP/s for the
-    gate/up GEMM) times the fill of the last tile break even.
+def choose_block_m(capacity: int, top_k: int, local_experts: int, fp8: bool = False) -> int:
+    """Token rows per GEMM tile from the expected rows per expert under even routing (``R * C * K`` entries over
+    ``R * L`` experts): 64 for decode, 128 from 36 expected rows, 256 from 80.
 
-    The expectation is the one under even routing: ``R * C * K`` entries over ``R * L`` experts.
+    Measured on 72 local experts (whole layer, us, narrower / wider tile): 28 rows 468 / 480, 43 rows 514 / 495,
+    57 rows 557 / 505, 85 rows 705 / 583 (64 / 128); 85 rows 588 / 568, 114 rows 663 / 591, 171 rows 854 / 700,
+    341 rows 1393 / 1155 (128 / 256).  A wider tile keeps an expert's rows in one tile (one pass over its weights)
+    and, at 256 rows, halves the operand bytes per flop that a CTA pulls from L2.
+
+    ``fp8``: the layer will hold block-scaled e4m3 experts.  Their kernels take tiles of up to 128 rows (128 from 96
+    expected rows), and 256-row tiles mean expanding the experts to bf16 in every forward, which pays from about
+    512 expected rows per expert on.
     """
     expected = (capacity * top_k) / max(local_experts, 1)
-    return 256 if expected >= 384 else 128 if expected >= 96 else 64
+    if fp8:
+        return 256 if expected >= 512 else 128 if expected >= 96 else 64
+    return 256 if expected >= 80 else 128 if expected >= 36 else 64
 
 
 def choose_meta_ctas(slot_words: int, n_sms: int) -> int:

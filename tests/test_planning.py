@@ -10,12 +10,19 @@ from moeflow_b200.fixed import choose_block_m, choose_meta_ctas
 def test_tile_rows_follow_the_expected_rows_per_expert_not_the_worst_case():
     assert choose_block_m(128, 8, 288) == 64     # EP=1 decode: 3.5 rows per expert
     assert choose_block_m(128, 8, 36) == 64      # EP=8, T=128: 28 rows per expert (worst case would be 227)
-    assert choose_block_m(2048, 8, 144) == 128   # EP=2 prefill: 114 rows per expert
+    assert choose_block_m(256, 8, 36) == 128     # 57 rows per expert: one tile per expert instead of two for some
+    assert choose_block_m(512, 8, 72) == 128     # 57 rows
+    assert choose_block_m(512, 8, 144) == 64     # 28 rows
+    assert choose_block_m(2048, 8, 144) == 256   # EP=2 prefill: 114 rows per expert
     assert choose_block_m(8192, 8, 36) == 256    # EP=8 long prefill: 1820 rows per expert
-    assert choose_block_m(8192, 8, 144) == 256   # EP=2 long prefill: 455 rows per expert
-    assert choose_block_m(4096, 8, 144) == 128   # 228 rows per expert
-    assert choose_block_m(512, 8, 144) == 64
     assert choose_block_m(1, 8, 1) == 64
+
+
+def test_tile_rows_for_layers_that_will_hold_e4m3_experts():
+    assert choose_block_m(256, 8, 36, fp8=True) == 64      # 57 rows
+    assert choose_block_m(2048, 8, 144, fp8=True) == 128   # 114 rows: the e4m3 kernels, no expansion
+    assert choose_block_m(8192, 8, 144, fp8=True) == 128   # 455 rows
+    assert choose_block_m(8192, 8, 36, fp8=True) == 256    # 1820 rows: expanded to bf16 per forward
 
 
 def test_metadata_ctas_by_size():
