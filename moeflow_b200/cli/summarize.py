@@ -1,10 +1,11 @@
 """Turn benchmark records into Markdown tables; refuses records that are incomplete or unvalidated.
 
     python -m moeflow_b200.cli.summarize layer  results/layer_*.json
-    python -m moeflow_b200.cli.summarize ab     results/ab_*.json
+    python -m moeflow_b200.cli.summarize ab     results/ab_*.json        # ab_fixed and ab_native_fixed records
     python -m moeflow_b200.cli.summarize stages results/stages_*.json
     python -m moeflow_b200.cli.summarize logits native.json candidate.json
     python -m moeflow_b200.cli.summarize serving w1_native.json w1_moeflow.json --requests 16 --input-len 1024 --output-len 1024 --concurrency 4
+    python -m moeflow_b200.cli.summarize decode  results/decode_*.json   # self-contained decoder (cli/decode_bench.py)
     python -m moeflow_b200.cli.summarize launches launches.csv      # kernels per forward from an ncu launch list
 
 Counterpart of the reference's ``scripts/summarize_{ablations,backend_pair,logits,replay_trace,stage1,w1}.py``.
@@ -20,10 +21,11 @@ from collections import Counter
 from pathlib import Path
 
 
-def load(path: str, kind: str | None = None) -> dict:
+def load(path: str, kind: str | tuple[str, ...] | None = None) -> dict:
     rec = json.loads(Path(path).read_text())
-    if kind is not None and rec.get("kind") != kind:
-        raise SystemExit(f"{path}: expected a {kind} record, found {rec.get('kind')!r}")
+    kinds = (kind,) if isinstance(kind, str) else kind
+    if kinds is not None and rec.get("kind") not in kinds:
+        raise SystemExit(f"{path}: expected a {' or '.join(kinds)} record, found {rec.get('kind')!r}")
     if rec.get("complete") is False:
         raise SystemExit(f"{path}: record is incomplete; refusing to summarise it")
     return rec
@@ -47,7 +49,7 @@ def layer_table(paths: list[str]) -> str:
 def ab_table(paths: list[str]) -> str:
     rows = ["| A | B | EP | T | A median us | B median us | gain us | 95% CI of (B-A) | significant | beneficial |", "|---|---|---:|---:|---:|---:|---:|---|---|---|"]
     for p in paths:
-        rec = load(p, "ab_fixed")
+        rec = load(p, ("ab_fixed", "ab_native_fixed"))  # same shape: fused variants, or native transport vs fused
         c = rec["config"]
         for pt in rec["results"]["points"]:
             if not (pt["gate"]["a"]["passed"] and pt["gate"]["b"]["passed"]):
@@ -95,6 +97,23 @@ def serving_table(paths: list[str], requests, input_len, output_len, concurrency
     return "\n".join(rows)
 
 
+def decode_table(paths: list[str]) -> str:
+    """TPOT / throughput of the self-contained decoder (``cli/decode_bench.py`` records); a point whose layer status
+    is not ok or whose output is not finite makes the whole table refuse."""
+    rows = ["| layers | EP | experts | concurrency | sequences per rank | TPOT median ms | p95 ms | tokens/s |",
+            "|---:|---:|---|---:|---:|---:|---:|---:|"]
+    for p in paths:
+        rec = load(p, "decode_bench")
+        c = rec["config"]
+        for pt in rec["results"]["points"]:
+            if pt["status"]["code"] != 0 or not pt["finite"]:
+                raise SystemExit(f"{p}: a point ended with status {pt['status']['name']!r} or a non-finite output; no table")
+            rows.append(f"| {c['layers']} | {c['world']} | {'e4m3' if c.get('fp8') else 'bf16'} | {pt['concurrency']} | "
+                        f"{pt['batch_per_rank']} | {pt['tpot_ms']['median']:.3f} | {pt['tpot_ms']['p95']:.3f} | "
+                        f"{pt['tokens_per_second']:.0f} |")
+    return "\n".join(rows)
+
+
 def launches_summary(path: str, forwards: int | None = None) -> str:
     """Kernel launches per forward from a launch list written by
     ``ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file <path> <command>`` (one pass per
@@ -119,7 +138,7 @@ def launches_summary(path: str, forwards: int | None = None) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("what", choices=["layer", "ab", "stages", "logits", "serving", "launches"])
+    ap.add_argument("what", choices=["layer", "ab", "stages", "logits", "serving", "decode", "launches"])
     ap.add_argument("paths", nargs="+")
     ap.add_argument("--requests", type=int)
     ap.add_argument("--input-len", type=int)
@@ -135,6 +154,8 @@ def main() -> None:
         print(stages_table(args.paths))
     elif args.what == "logits":
         print(logits_summary(*args.paths[:2]))
+    elif args.what == "decode":
+        print(decode_table(args.paths))
     elif args.what == "serving":
         print(serving_table(args.paths, args.requests, args.input_len, args.output_len, args.concurrency))
     else:

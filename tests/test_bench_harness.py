@@ -307,3 +307,30 @@ def test_headline_bench_clock_summary_and_cli_defaults():
     ]
     summary = sampler.stop()
     assert summary == {"sm_mhz": 1410.0, "sm_max_mhz": 1965.0, "power_w_max": 998.0, "samples": 3, "reasons": ["sw_power_cap"]}
+
+
+def test_pair_and_decode_tables(tmp_path):
+    gate = {"a": {"passed": True}, "b": {"passed": True}}
+    paired = {"median_improvement": 28.7, "ci95": [-30.1, -27.0], "significant": True, "beneficial": True}
+    pt = {"tokens": 1, "gate": gate, "a_us": {"median": 141.9}, "b_us": {"median": 113.2}, "paired": paired}
+    rec = make_record("ab_native_fixed", {"a": "vllm_agrs", "b": "fused", "world": 2}, {"points": [pt]})
+    good = write_record(tmp_path / "pair.json", rec)
+    assert "| vllm_agrs | fused | 2 | 1 | 141.9 | 113.2 | +28.7 |" in S.ab_table([str(good)])
+    failed = write_record(tmp_path / "pair_failed.json", make_record(
+        "ab_native_fixed", {"a": "vllm_agrs", "b": "fused", "world": 2},
+        {"points": [{**pt, "gate": {"a": {"passed": True}, "b": {"passed": False}}}]}))
+    with pytest.raises(SystemExit):
+        S.ab_table([str(failed)])
+
+    dpt = {"concurrency": 4, "batch_per_rank": 1, "tpot_ms": {"median": 8.7456, "p95": 8.7579}, "tokens_per_second": 457.4,
+           "status": {"code": 0, "name": "ok"}, "finite": True}
+    drec = make_record("decode_bench", {"layers": 42, "world": 4, "fp8": True}, {"points": [dpt]})
+    dgood = write_record(tmp_path / "decode.json", drec)
+    assert "| 42 | 4 | e4m3 | 4 | 1 | 8.746 | 8.758 | 457 |" in S.decode_table([str(dgood)])
+    dbad = write_record(tmp_path / "decode_bad.json", make_record(
+        "decode_bench", {"layers": 42, "world": 4, "fp8": False},
+        {"points": [{**dpt, "status": {"code": 3, "name": "dispatch flag wait ran out"}}]}))
+    with pytest.raises(SystemExit):
+        S.decode_table([str(dbad)])
+    with pytest.raises(SystemExit):
+        S.decode_table([str(good)])  # wrong kind
