@@ -658,7 +658,15 @@ class FixedEPLayer:
         pack["tm2"] = make_weight_tmap(pack["w2"].view(torch.uint8))
         return pack
 
-    _expand_scratch: dict = {}  # (device index, L, I, H) -> bf16 weight scratch + tensor maps, shared between layers
+    # (device index, L, I, H) -> bf16 weight scratch + tensor maps.  Shared by every layer of that shape on the device:
+    # each forward rewrites it before its GEMMs, so forwards that use it must be ordered on one stream (they are: a
+    # decoder runs its layers one after the other).  `release_expand_scratch()` frees it.
+    _expand_scratch: dict = {}
+
+    @classmethod
+    def release_expand_scratch(cls) -> None:
+        """Drop the bf16 expansion scratch of all shapes (layers bound to e4m3 packs rebuild it on their next bind)."""
+        cls._expand_scratch.clear()
 
     def _expanded_weights(self) -> dict:
         from .ops.kernels import make_weight_tmap
